@@ -1,0 +1,284 @@
+// Shared device/host helpers for the sm_100a layer kernels.
+//
+// Everything here is header-only and internal to the library; the public
+// surface is include/b200_layer_kernels.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// host side: error reporting, device properties, tunables
+// ---------------------------------------------------------------------------
+
+// Reports a usage / runtime error.  Default mode mirrors the reference's
+// convention (src/nn.h:13-52): print to stderr and exit(1).  In record mode the
+// message is kept and the launcher returns without launching.
+void report_error(const char* file, int line, const char* fmt, ...);
+
+#define B200_REQUIRE(cond, ...)                                  \
+    do {                                                         \
+        if (!(cond)) {                                           \
+            ::b200::report_error(__FILE__, __LINE__, __VA_ARGS__); \
+            return;                                              \
+        }                                                        \
+    } while (0)
+
+#define B200_CUDA_OK(call)                                                            \
+    do {                                                                              \
+        cudaError_t e_ = (call);                                                      \
+        if (e_ != cudaSuccess) {                                                      \
+            ::b200::report_error(__FILE__, __LINE__, "%s -> %s", #call, cudaGetErrorString(e_)); \
+            return;                                                                   \
+        }                                                                             \
+    } while (0)
+
+// Checks the launch status of the kernel that was just enqueued.
+#define B200_CHECK_LAUNCH()                                                           \
+    do {                                                                              \
+        cudaError_t e_ = cudaPeekAtLastError();                                       \
+        if (e_ != cudaSuccess) {                                                      \
+            (void)cudaGetLastError();                                                 \
+            ::b200::report_error(__FILE__, __LINE__, "kernel launch failed: %s", cudaGetErrorString(e_)); \
+        }                                                                             \
+    } while (0)
+
+int sm_count();              // SMs of the current device (cached per device)
+int tune_get(const char* key, int dflt);  // value set through b200_tune_set, else dflt
+void count_launch(int n = 1);  // increments the library's launch counter
+
+// Scratch memory owned by the library, one arena per (device, stream).  Grows
+// on demand (allocation happens only when a call needs more than is reserved);
+// the contents are zero when first handed out and kernels that use counters
+// restore them to zero before they finish.
+struct Scratch {
+    float* partials;       // at least `floats` floats
+    unsigned int* tickets; // at least `ntickets` counters, all zero between kernels
+};
+bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out);
+// Device address of the error word that kernels set when a bounded wait runs
+// out (0 = healthy); one word per device.
+int* device_error_word();
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------------------
+// device side
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// W consecutive floats moved as one access (W = 1 or 4).
+template <int W>
+struct alignas(4 * W) Pack {
+    float v[W];
+};
+
+// Streaming (evict-first) loads and stores: every tensor on this path is
+// touched once per kernel, so nothing is worth keeping in L1/L2.
+template <int W>
+__device__ __forceinline__ Pack<W> load_stream(const float* p)
+{
+    Pack<W> r;
+    if constexpr (W == 4) {
+        float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+        r.v[0] = __ldcs(p);
+    }
+    return r;
+}
+
+template <int W>
+__device__ __forceinline__ void store_stream(float* p, const Pack<W>& r)
+{
+    if constexpr (W == 4) {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(r.v[0], r.v[1], r.v[2], r.v[3]));
+    } else {
+        __stcs(p, r.v[0]);
+    }
+}
+
+// Cached loads for small, re-used operands (gamma, beta, statistics).
+template <int W>
+__device__ __forceinline__ Pack<W> load_cached(const float* p)
+{
+    Pack<W> r;
+    if constexpr (W == 4) {
+        float4 t = __ldg(reinterpret_cast<const float4*>(p));
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+        r.v[0] = __ldg(p);
+    }
+    return r;
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Sum over the whole CTA; every thread gets the result.  `buf` holds >= 32
+// floats of shared memory and may be reused right after the call returns.
+__device__ __forceinline__ float cta_sum(float v, float* buf)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // protects buf against a previous call's readers
+    if (lane == 0)
+        buf[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? buf[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+// --- activations -----------------------------------------------------------
+// The reference's SiLU/GELU/tanh are built on a clamped (7,6) rational
+// approximation of tanh (src/kernels.cu:6-17), which is part of its numerics;
+// it is reproduced term for term (with a correctly rounded division).
+enum : int { ACT_IDENTITY = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SILU = 3, ACT_TANH = 4, ACT_MP_SILU = 5 };
+
+__device__ __forceinline__ float rational_tanh(float x)
+{
+    const float x2 = x * x;
+    const float num = x * (135135.0f + x2 * (17325.0f + x2 * (378.0f + x2)));
+    const float den = 135135.0f + x2 * (62370.0f + x2 * (3150.0f + x2 * 28.0f));
+    return fmaxf(-1.0f, fminf(1.0f, num / den));
+}
+
+__device__ __forceinline__ float rational_sigmoid(float x)
+{
+    return fmaxf(0.0f, fminf(1.0f, (rational_tanh(x * 0.5f) + 1.0f) * 0.5f));
+}
+
+#define B200_MP_SILU_SCALE (1.0f / 0.596f)
+
+template <int ACT>
+__device__ __forceinline__ float act_value(float v)
+{
+    if constexpr (ACT == ACT_RELU) {
+        return v > 0.0f ? v : 0.0f;
+    } else if constexpr (ACT == ACT_GELU) {
+        return 0.5f * v * (1.0f + rational_tanh(0.7978845608f * (v + 0.044715f * v * v * v)));
+    } else if constexpr (ACT == ACT_SILU) {
+        return v * rational_sigmoid(v);
+    } else if constexpr (ACT == ACT_MP_SILU) {
+        return v * rational_sigmoid(v) * B200_MP_SILU_SCALE;
+    } else if constexpr (ACT == ACT_TANH) {
+        return rational_tanh(v);
+    } else {
+        return v;
+    }
+}
+
+// derivative with respect to the pre-activation z (src/kernels.cu:40-68)
+template <int ACT>
+__device__ __forceinline__ float act_slope(float z)
+{
+    if constexpr (ACT == ACT_RELU) {
+        return z > 0.0f ? 1.0f : 0.0f;
+    } else if constexpr (ACT == ACT_TANH) {
+        const float t = rational_tanh(z);
+        return 1.0f - t * t;
+    } else if constexpr (ACT == ACT_SILU) {
+        const float s = rational_sigmoid(z);
+        return s * (1.0f + z * (1.0f - s));
+    } else if constexpr (ACT == ACT_MP_SILU) {
+        const float s = rational_sigmoid(z);
+        return s * (1.0f + z * (1.0f - s)) * B200_MP_SILU_SCALE;
+    } else if constexpr (ACT == ACT_GELU) {
+        const float c = 0.7978845608f;
+        const float u = c * (z + 0.044715f * z * z * z);
+        const float t = rational_tanh(u);
+        const float du = c * (1.0f + 3.0f * 0.044715f * z * z);
+        return 0.5f * (1.0f + t) + 0.5f * z * (1.0f - t * t) * du;
+    } else {
+        return 1.0f;
+    }
+}
+
+// --- mbarrier / bulk tensor copy (TMA) primitives ----------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init_fence()
+{
+    // make the initialised barriers visible to the async (TMA) proxy
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity)
+{
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after ~2^22 polls (seconds at the very most), records
+// the failure in the library's device error word (`err`) and returns false so
+// the caller can unwind.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* err)
+{
+    for (unsigned it = 0; it < (1u << 22); ++it) {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if (it > 64)
+            __nanosleep(64);
+    }
+    atomicExch(err, 1);
+    return false;
+}
+
+// 2-D tile, global -> this CTA's shared memory, completion counted on `bar`.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(smem_dst)), "l"(tmap), "r"(smem_addr(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// 2-D tile, shared -> global, tracked by the bulk async-group of this thread.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+        ::"l"(tmap), "r"(smem_addr(smem_src)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// generic-proxy writes to shared memory become visible to the async proxy
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+#endif  // __CUDACC__
+
+}  // namespace b200

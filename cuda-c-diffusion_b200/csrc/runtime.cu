@@ -1,0 +1,208 @@
+// Host-side runtime of the layer-kernel library: error reporting, tunables,
+// launch counter, per-(device, stream) scratch arenas.
+#include "dev_common.cuh"
+#include "../../include/b200_layer_kernels.h"
+
+#include <map>
+#include <mutex>
+#include <stdarg.h>
+#include <string>
+#include <string.h>
+#include <utility>
+#include <vector>
+
+namespace b200 {
+
+__device__ int g_device_error = 0;
+
+int* device_error_word()
+{
+    static int* cached[64] = { nullptr };
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return nullptr;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_error) != cudaSuccess)
+            return nullptr;
+        cached[dev] = static_cast<int*>(p);
+    }
+    return cached[dev];
+}
+
+static std::mutex g_mu;
+static int g_error_mode = 0;
+static int g_error_count = 0;
+static std::string g_last_error;
+static std::map<std::string, int> g_tunables;
+static long long g_launches = 0;
+
+void report_error(const char* file, int line, const char* fmt, ...)
+{
+    char msg[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(msg, sizeof msg, fmt, ap);
+    va_end(ap);
+    const char* base = strrchr(file, '/');
+    char full[640];
+    snprintf(full, sizeof full, "b200 layer kernels %s:%d: %s", base ? base + 1 : file, line, msg);
+    int mode;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_last_error = full;
+        ++g_error_count;
+        mode = g_error_mode;
+    }
+    if (mode == 0) {
+        fprintf(stderr, "%s\n", full);
+        exit(1);
+    }
+}
+
+int sm_count()
+{
+    static int cached[64] = { 0 };
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int tune_get(const char* key, int dflt)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_tunables.find(key);
+    return it == g_tunables.end() ? dflt : it->second;
+}
+
+void count_launch(int n)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_launches += n;
+}
+
+// --- scratch arenas ----------------------------------------------------------
+struct Arena {
+    float* partials = nullptr;
+    size_t floats = 0;
+    unsigned int* tickets = nullptr;
+    size_t ntickets = 0;
+};
+static std::map<std::pair<int, cudaStream_t>, Arena> g_arenas;
+
+bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess)
+        return false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    Arena& a = g_arenas[std::make_pair(dev, s)];
+    if (a.floats < floats) {
+        // Growing: the old block may still be in use by kernels in flight on
+        // this stream, so it is released with the stream-ordered free.
+        size_t want = floats < (1u << 18) ? (1u << 18) : floats;
+        float* np = nullptr;
+        if (cudaMalloc(&np, want * sizeof(float)) != cudaSuccess)
+            return false;
+        if (a.partials)
+            cudaFreeAsync(a.partials, s);
+        a.partials = np;
+        a.floats = want;
+    }
+    if (a.ntickets < ntickets) {
+        size_t want = ntickets < 4096 ? 4096 : ntickets;
+        unsigned int* nt = nullptr;
+        if (cudaMalloc(&nt, want * sizeof(unsigned int)) != cudaSuccess)
+            return false;
+        if (cudaMemsetAsync(nt, 0, want * sizeof(unsigned int), s) != cudaSuccess)
+            return false;
+        if (a.tickets)
+            cudaFreeAsync(a.tickets, s);
+        a.tickets = nt;
+        a.ntickets = want;
+    }
+    out->partials = a.partials;
+    out->tickets = a.tickets;
+    return true;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void b200_set_error_mode(int mode)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_error_mode = mode ? 1 : 0;
+}
+
+int b200_error_count(void)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_error_count;
+}
+
+int b200_last_error(char* buf, int buflen)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (buf && buflen > 0) {
+        strncpy(buf, g_last_error.c_str(), (size_t)buflen - 1);
+        buf[buflen - 1] = 0;
+    }
+    return (int)g_last_error.size();
+}
+
+void b200_clear_error(void)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_error_count = 0;
+    g_last_error.clear();
+}
+
+int b200_device_error_status(void)
+{
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess)
+        return -1;
+    return v;
+}
+
+long long b200_launch_count(void)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_launches;
+}
+
+void b200_launch_count_reset(void)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_launches = 0;
+}
+
+int b200_scratch_reserve(cudaStream_t s, long long bytes)
+{
+    Scratch sc;
+    size_t floats = bytes > 0 ? (size_t)((bytes + 3) / 4) : 0;
+    return scratch_get(s, floats, 4096, &sc) ? 0 : -1;
+}
+
+void b200_tune_set(const char* key, int value)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_tunables[key] = value;
+}
+
+int b200_tune_get(const char* key, int dflt) { return tune_get(key, dflt); }
+
+const char* b200_version(void) { return "b200-layer-kernels 0.1 (sm_100a)"; }
+
+}  // extern "C"

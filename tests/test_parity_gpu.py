@@ -1,0 +1,265 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle
+and against the reference's own kernels rebuilt for sm_100a (A/B), on the same
+seeded inputs.  Tolerances are the stated fp32 ones: forward rel <= 1e-5,
+backward rel <= 1e-4 (cases.TOL_FWD / TOL_BWD), relative to the largest
+reference magnitude of the tensor."""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+EXTRA = [
+    ("pixel_norm_128", "pixel_norm", dict(rows=77, C=128, eps=1e-4)),
+    ("pixel_norm_24", "pixel_norm", dict(rows=9, C=24, eps=1e-4)),
+    ("layernorm_384", "layernorm", dict(rows=70, C=384)),
+    ("layernorm_1024", "layernorm", dict(rows=19, C=1024)),
+    ("layernorm_100", "layernorm", dict(rows=300, C=100)),
+    ("groupnorm_cluster", "groupnorm", dict(B=3, HW=256, C=64, G=8, act=None)),
+    ("groupnorm_mp_silu", "groupnorm", dict(B=2, HW=196, C=128, G=32, act="mp_silu")),
+    ("groupnorm_relu", "groupnorm", dict(B=1, HW=64, C=16, G=2, act="relu")),
+    ("groupnorm_wide", "groupnorm", dict(B=2, HW=1024, C=256, G=32, act="silu")),
+    ("groupnorm_cpg1", "groupnorm", dict(B=2, HW=100, C=32, G=32, act=None)),
+    ("groupnorm_96", "groupnorm", dict(B=2, HW=64, C=96, G=32, act=None)),
+    ("weight_norm_big", "weight_norm", dict(rows=1152, cols=128, eps=1e-4)),
+    ("weight_norm_tall", "weight_norm", dict(rows=2500, cols=20, eps=1e-4)),
+    ("weight_norm_tiny", "weight_norm", dict(rows=3, cols=4, eps=1e-4)),
+    ("adam_ema_odd", "adam_ema", dict(n=4099, steps=2, decay=0.99)),
+    ("mp_cat_wide", "mp_cat", dict(rows=513, Ca=128, Cb=64, t=0.7)),
+]
+ALL = cases.CASES + EXTRA
+
+
+def _check(got, ref, name, skip=()):
+    for k, r in ref.items():
+        if k in skip or k == "y64":
+            continue
+        e = cases.rel_err(got[k], r)
+        assert e <= cases.tolerance(k), f"{name}:{k} rel err {e:.3e} > {cases.tolerance(k):.0e}"
+
+
+def _embedding_check(got, ref64, tmax, name):
+    # sin/cos of an fp32 argument of magnitude A carries an absolute error of about
+    # A * 2^-23 from rounding the argument alone; allow a few units of that.
+    tol = 4.0 * max(tmax, 1.0) * 2.0 ** -23 + 2e-6
+    err = float(np.max(np.abs(got.astype(np.float64) - ref64)))
+    assert err <= tol, f"{name}: abs err {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("name,op,p", ALL, ids=[c[0] for c in ALL])
+def test_matches_oracle(lib, orc, name, op, p):
+    inp = cases.make_inputs(op, p, seed=cases.seed_of(name))
+    ref = cases.oracle_run(orc, op, p, inp)
+    got = cases.gpu_run(lib, op, p, inp, fused=True)
+    if op == "mp_fourier":
+        _embedding_check(got["y"], ref["y64"], 2 * math.pi * 4.0, name)
+    elif op == "sinusoidal":
+        _embedding_check(got["y"], ref["y64"], p["tmax"], name)
+    else:
+        _check(got, ref, name)
+
+
+REF_CASES = [c for c in ALL if c[1] != "pixel_norm"]
+
+
+@pytest.mark.parametrize("name,op,p", REF_CASES, ids=[c[0] for c in REF_CASES])
+def test_matches_reference_kernels(lib, ref_lib, ref_lib_precise, name, op, p):
+    """A/B against the reference's kernels.cu built for this GPU.  Embeddings use the
+    build without --use_fast_math: the fast intrinsics are off by far more than
+    the tolerance at these arguments."""
+    inp = cases.make_inputs(op, p, seed=cases.seed_of(name))
+    got = cases.gpu_run(lib, op, p, inp, fused=True)
+    if op in ("mp_fourier", "sinusoidal"):
+        ref = cases.gpu_run(ref_lib_precise, op, p, inp, fused=False)
+        tmax = p.get("tmax", 2 * math.pi * 4.0)
+        _embedding_check(got["y"], ref["y"].astype(np.float64), 2 * tmax, name)
+        return
+    ref = cases.gpu_run(ref_lib, op, p, inp, fused=False)
+    _check(got, ref, name)
+
+
+def test_oracle_agrees_with_reference_kernels(orc, ref_lib):
+    """Pins the CPU restatement to the reference itself on every non-embedding case."""
+    for name, op, p in cases.CASES:
+        if op in ("mp_fourier", "sinusoidal"):
+            continue
+        inp = cases.make_inputs(op, p, seed=cases.seed_of(name))
+        _check(cases.oracle_run(orc, op, p, inp), cases.gpu_run(ref_lib, op, p, inp, fused=False), "oracle/" + name)
+
+
+# ----------------------------------------------------------------------------- edge cases
+def _t(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).cuda()
+
+
+def _st():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _pp(t, off=0):
+    return ctypes.c_void_p(t.data_ptr() + 4 * off)
+
+
+def test_empty_and_single_element(lib):
+    import torch
+    x = torch.ones(8, device="cuda")
+    y = torch.zeros(8, device="cuda")
+    lib.launch_activation_forward(_pp(y), _pp(x), 0, 3, _st())
+    lib.launch_weighted_sum(_pp(y), _pp(x), _pp(x), ctypes.c_float(1), ctypes.c_float(1), 0, _st())
+    lib.launch_groupnorm_forward(_pp(y), _pp(y), _pp(y), _pp(x), _pp(x), _pp(x), 0, 4, 4, 2, ctypes.c_float(1e-5), _st())
+    torch.cuda.synchronize()
+    assert float(y.abs().sum()) == 0.0
+    lib.launch_activation_forward(_pp(y), _pp(x), 1, 1, _st())
+    torch.cuda.synchronize()
+    assert y[0].item() == 1.0 and float(y[1:].abs().sum()) == 0.0
+
+
+def test_misaligned_pointers_take_the_scalar_path(lib, orc):
+    import torch
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal(1027, dtype=np.float32)
+    b = rng.standard_normal(1027, dtype=np.float32)
+    ta, tb = _t(a), _t(b)
+    out = torch.zeros(1027, device="cuda")
+    n = 1021
+    lib.launch_weighted_sum(_pp(out, 3), _pp(ta, 1), _pp(tb, 2), ctypes.c_float(0.5), ctypes.c_float(2.0), n, _st())
+    torch.cuda.synchronize()
+    ref = orc.weighted_sum(a[1:1 + n], b[2:2 + n], 0.5, 2.0)
+    got = out.cpu().numpy()
+    assert cases.rel_err(got[3:3 + n], ref) <= 1e-6
+    assert np.all(got[:3] == 0) and np.all(got[3 + n:] == 0)
+    # misaligned groupnorm falls back to the generic kernels and still matches
+    B, HW, C, G = 2, 64, 32, 4
+    x = rng.standard_normal(B * HW * C + 1, dtype=np.float32)
+    gam = rng.standard_normal(C, dtype=np.float32); bet = rng.standard_normal(C, dtype=np.float32)
+    tx, tg, tbt = _t(x), _t(gam), _t(bet)
+    y = torch.zeros(B * HW * C + 1, device="cuda"); mu = torch.zeros(B * G, device="cuda"); rs = torch.zeros(B * G, device="cuda")
+    lib.launch_groupnorm_forward(_pp(y, 1), _pp(mu), _pp(rs), _pp(tx, 1), _pp(tg), _pp(tbt), B, HW, C, G,
+                                 ctypes.c_float(1e-5), _st())
+    torch.cuda.synchronize()
+    ry, rmu, rrs = orc.groupnorm_forward(x[1:].reshape(B, HW, C), gam, bet, G, 1e-5)
+    assert cases.rel_err(y.cpu().numpy()[1:], ry.ravel()) <= 1e-5
+
+
+def test_aliased_operands_of_weighted_sum(lib, orc):
+    """out==a (ema.c:32, unet.c:247) and a==b (edm.c:57) are legal in the reference."""
+    import torch
+    rng = np.random.default_rng(6)
+    a = rng.standard_normal(5000, dtype=np.float32); b = rng.standard_normal(5000, dtype=np.float32)
+    ta, tb = _t(a), _t(b)
+    lib.launch_weighted_sum(_pp(ta), _pp(ta), _pp(tb), ctypes.c_float(0.999), ctypes.c_float(0.001), 5000, _st())
+    torch.cuda.synchronize()
+    assert cases.rel_err(ta.cpu().numpy(), orc.weighted_sum(a, b, 0.999, 0.001)) <= 1e-6
+    tb2 = _t(b)
+    lib.launch_weighted_sum(_pp(tb2), _pp(tb2), _pp(tb2), ctypes.c_float(0.25), ctypes.c_float(0.5), 5000, _st())
+    torch.cuda.synchronize()
+    assert cases.rel_err(tb2.cpu().numpy(), orc.weighted_sum(b, b, 0.25, 0.5)) <= 1e-6
+
+
+def test_backward_overwrites_parameter_gradients_and_is_deterministic(lib):
+    """Parameter gradients are overwritten (never accumulated) and two runs are bit-identical."""
+    import torch
+    name, op, p = "gn_det", "groupnorm", dict(B=6, HW=196, C=64, G=32, act="silu")
+    inp = cases.make_inputs(op, p, seed=11)
+    r1 = cases.gpu_run(lib, op, p, inp, fused=True)
+    r2 = cases.gpu_run(lib, op, p, inp, fused=True)
+    for k in r1:
+        assert np.array_equal(r1[k], r2[k]), k
+    name, op, p = "ln_det", "layernorm", dict(rows=1000, C=256)
+    inp = cases.make_inputs(op, p, seed=12)
+    r1 = cases.gpu_run(lib, op, p, inp, fused=True)
+    r2 = cases.gpu_run(lib, op, p, inp, fused=True)
+    for k in r1:
+        assert np.array_equal(r1[k], r2[k]), k
+
+
+def test_tile_and_generic_groupnorm_agree(lib, orc):
+    p = dict(B=4, HW=196, C=64, G=32, act="silu")
+    inp = cases.make_inputs("groupnorm", p, seed=21)
+    tile = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    lib.b200_tune_set(b"gn_force_generic", 1)
+    try:
+        gen = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        lib.b200_tune_set(b"gn_force_generic", 0)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    _check(tile, ref, "tile")
+    _check(gen, ref, "generic")
+
+
+@pytest.mark.parametrize("ct,cs", [(8, 1), (16, 2), (32, 4), (64, 4), (64, 1), (32, 2)])
+def test_groupnorm_tile_geometries(lib, orc, ct, cs):
+    """Every (channel tile, cluster size) the heuristic may choose gives the same answer."""
+    p = dict(B=3, HW=196, C=64, G=32, act="mp_silu")
+    inp = cases.make_inputs("groupnorm", p, seed=31)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    for key in (b"gn_fwd_ct", b"gn_bwd_ct"):
+        lib.b200_tune_set(key, ct)
+    for key in (b"gn_fwd_cs", b"gn_bwd_cs"):
+        lib.b200_tune_set(key, cs)
+    try:
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs"):
+            lib.b200_tune_set(key, 0)
+    _check(got, ref, f"ct{ct}cs{cs}")
+
+
+def test_multi_tensor_entry_points(pkg, lib, orc):
+    import importlib
+    import torch
+    ops = importlib.import_module("cuda-c-diffusion_b200.ops")
+    rng = np.random.default_rng(41)
+    sizes = [1, 7, 4096, 1, 73728, 128, 1, 36864]
+    P = [rng.standard_normal(n, dtype=np.float32) * 0.02 for n in sizes]
+    Gd = [rng.standard_normal(n, dtype=np.float32) * 1e-3 for n in sizes]
+    tp = [_t(x) for x in P]; tg = [_t(x) for x in Gd]
+    tm = [torch.zeros_like(x) for x in tp]; tv = [torch.zeros_like(x) for x in tp]; ts = [x.clone() for x in tp]
+    ts[1] = None  # a tensor without EMA shadow
+    bc1, bc2 = cases._bias_corrections(1)
+    ops.adam_ema_step_multi_(zip(tp, tg, tm, tv, ts), 1e-3, 0.9, 0.999, 1e-8, bc1, bc2, 0.999, 0.5)
+    torch.cuda.synchronize()
+    for i, n in enumerate(sizes):
+        rp, rm, rv, rsh = orc.adam_ema_step(P[i], np.zeros(n, np.float32), np.zeros(n, np.float32), P[i], Gd[i], 1e-3,
+                                            0.9, 0.999, 1e-8, bc1, bc2, 0.999, 0.5)
+        assert cases.rel_err(tp[i].cpu().numpy(), rp) <= 1e-5, i
+        assert cases.rel_err(tm[i].cpu().numpy(), rm) <= 1e-5, i
+        assert cases.rel_err(tv[i].cpu().numpy(), rv) <= 1e-5, i
+        if ts[i] is not None:
+            assert cases.rel_err(ts[i].cpu().numpy(), rsh) <= 1e-5, i
+    shapes = [(1152, 128), (64, 128), (576, 64), (9, 64), (30, 6)]
+    Ws = [rng.standard_normal(s, dtype=np.float32) for s in shapes]
+    tw = [_t(w) for w in Ws]
+    ops.weight_normalize_multi_(tw, 1e-4)
+    torch.cuda.synchronize()
+    for w, t in zip(Ws, tw):
+        assert cases.rel_err(t.cpu().numpy(), orc.weight_normalize(w, 1e-4)) <= 1e-5
+
+
+def test_axpby_rows_matches_per_sample_loop(lib, orc):
+    import torch
+    rng = np.random.default_rng(51)
+    rows, dim = 37, 784
+    a = rng.standard_normal((rows, dim), dtype=np.float32); b = rng.standard_normal((rows, dim), dtype=np.float32)
+    wa = rng.standard_normal(rows, dtype=np.float32); wb = rng.standard_normal(rows, dtype=np.float32)
+    ta, tb, twa, twb = _t(a), _t(b), _t(wa), _t(wb)
+    out = torch.empty_like(ta)
+    lib.launch_axpby_rows(_pp(out), _pp(ta), _pp(tb), _pp(twa), _pp(twb), rows, dim, _st())
+    loop = torch.empty_like(ta)
+    for r in range(rows):  # what diffusion/edm.c:56-58 does
+        lib.launch_weighted_sum(_pp(loop, r * dim), _pp(ta, r * dim), _pp(tb, r * dim), ctypes.c_float(float(wa[r])),
+                                ctypes.c_float(float(wb[r])), dim, _st())
+    torch.cuda.synchronize()
+    assert torch.equal(out, loop)
+    assert cases.rel_err(out.cpu().numpy(), orc.axpby_rows(a, b, wa, wb)) <= 1e-6
+
+
+def test_no_bounded_wait_ran_out(lib):
+    assert lib.b200_device_error_status() == 0
+    assert lib.b200_launch_count() > 0
