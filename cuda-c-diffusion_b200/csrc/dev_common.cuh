@@ -142,7 +142,10 @@ __device__ __forceinline__ float cta_sum(float v, float* buf)
 // --- activations -----------------------------------------------------------
 // The reference's SiLU/GELU/tanh are built on a clamped (7,6) rational
 // approximation of tanh (src/kernels.cu:6-17), which is part of its numerics;
-// it is reproduced term for term (with a correctly rounded division).
+// it is reproduced term for term.  The quotient uses the approximate divide
+// (2 ulp), which is also what the reference's own build (--use_fast_math)
+// executes; these kernels sit close enough to the issue-rate limit that the
+// ~8 extra instructions of a correctly rounded divide are measurable.
 enum : int { ACT_IDENTITY = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SILU = 3, ACT_TANH = 4, ACT_MP_SILU = 5 };
 
 __device__ __forceinline__ float rational_tanh(float x)
@@ -150,12 +153,15 @@ __device__ __forceinline__ float rational_tanh(float x)
     const float x2 = x * x;
     const float num = x * (135135.0f + x2 * (17325.0f + x2 * (378.0f + x2)));
     const float den = 135135.0f + x2 * (62370.0f + x2 * (3150.0f + x2 * 28.0f));
-    return fmaxf(-1.0f, fminf(1.0f, num / den));
+    return fmaxf(-1.0f, fminf(1.0f, __fdividef(num, den)));
 }
 
+// (tanh(x/2)+1)/2.  The reference clamps the result to [0,1] once more; with the
+// tanh already clamped to [-1,1] that second clamp can never change the value
+// ((t+1)*0.5 is exact at both ends and monotone), so it is not repeated here.
 __device__ __forceinline__ float rational_sigmoid(float x)
 {
-    return fmaxf(0.0f, fminf(1.0f, (rational_tanh(x * 0.5f) + 1.0f) * 0.5f));
+    return (rational_tanh(x * 0.5f) + 1.0f) * 0.5f;
 }
 
 #define B200_MP_SILU_SCALE (1.0f / 0.596f)

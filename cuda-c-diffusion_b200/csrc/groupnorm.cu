@@ -1,23 +1,26 @@
 // NHWC GroupNorm forward / backward, optionally fused with an activation
 // (reference: src/kernels.cu:622-745, composed with :103-117 by conv_residual.c).
 //
-// Tile kernels (the fast path).  x is viewed as a matrix [B*HW, C].  One CTA owns
-// the tile  [R rows of one sample] x [Ct channels]  where Ct covers whole groups;
-// a thread-block cluster of CS CTAs splits the HW rows of one sample, so the
-// cluster together holds every element of Ct/cpg groups of that sample in
-// shared memory.  Consequences:
-//   * x (and dy) cross HBM exactly once: bulk tensor copies (TMA) bring the
-//     tile in chunk by chunk, statistics and the normalised output are both
-//     produced from shared memory, and the result leaves through TMA stores;
-//   * statistics are accumulated while later chunks are still in flight;
-//   * group statistics are combined across the cluster through distributed
-//     shared memory (no global round trip, no atomics);
+// Tile kernels (the fast path).  x is viewed as a matrix [B*HW, C].  A work item
+// is (sample b, channel tile of Ct channels covering whole groups); a
+// thread-block cluster of CS CTAs splits the HW rows of the item, so the cluster
+// together holds every element of Ct/cpg groups of one sample in shared memory:
+//   * x (and dy) cross HBM exactly once: bulk tensor copies (TMA) bring a tile
+//     in, statistics and the result are both produced from shared memory, and
+//     the result leaves through TMA stores;
+//   * clusters are persistent and double-buffered: while item i is being
+//     reduced / normalised / stored, the loads of item i+1 are already in flight
+//     into the other buffer, so each SM keeps HBM requests outstanding through
+//     the synchronisation-heavy phases;
+//   * per-channel partial statistics are folded with warp shuffles, then across
+//     the cluster through distributed shared memory (no global round trip);
 //   * backward reuses the per-channel sums of dy and dy*xhat for BOTH the group
-//     sums that dx needs and the per-sample dgamma/dbeta partials; the last CTA
-//     of a channel tile (atomic ticket) adds the partials in a fixed order.
+//     sums that dx needs and the per-sample dgamma/dbeta partials; the last
+//     item of a channel tile (atomic ticket) adds the partials in a fixed order,
+//     so parameter gradients are overwritten and bit-reproducible.
 // Shapes the tile path cannot take (C % 4 != 0, no usable row chunking, a
 // sample tile larger than a cluster's shared memory, misaligned pointers) use
-// the generic kernels at the end of this file.
+// the generic kernels further down.
 #include "dev_common.cuh"
 #include "tma_desc.cuh"
 #include "../../include/b200_layer_kernels.h"
@@ -28,33 +31,42 @@ namespace cg = cooperative_groups;
 
 namespace b200 {
 
-constexpr int GN_THREADS = 256;
-constexpr int GN_MAX_CHUNKS = 32;
-constexpr int GN_RED_FLOATS = 2 * GN_THREADS * 4;  // two float4 per thread
+constexpr int GN_THREADS = 512;
+constexpr int GN_WARPS = GN_THREADS / 32;
+constexpr int GN_NBUF = 2;         // tile buffers per CTA (double buffering)
+constexpr int GN_MAX_CHUNKS = 8;   // TMA boxes per tile
+constexpr int GN_GENERIC_THREADS = 256;
 
 struct GnGeom {
     int HW, C, G, cpg;
-    int Ct;      // channels per tile (multiple of cpg and of 4)
-    int Q;       // Ct / 4 float4 columns
-    int RSTEP;   // row lanes = GN_THREADS / Q
-    int CS;      // cluster size: CTAs that split the HW rows of a sample
-    int R;       // rows per CTA = HW / CS
-    int RB;      // rows per TMA box
-    int nchunk;  // R / RB
-    int Gt;      // groups per tile = Ct / cpg
+    int Ct;        // channels per tile (multiple of cpg and of 4)
+    int Q;         // Ct / 4 float4 columns
+    int RSTEP;     // row lanes = GN_THREADS / Q
+    int CS;        // cluster size: CTAs that split the HW rows of an item
+    int R;         // rows per CTA = HW / CS
+    int RB;        // rows per TMA box
+    int nchunk;    // R / RB
+    int Gt;        // groups per tile = Ct / cpg
+    int nct;       // channel tiles per sample = C / Ct
+    int items;     // B * nct
+    int nclusters; // clusters in the grid (each loops over items)
+    int shuffle;   // 1: Q divides 32, row lanes of a warp are folded with shuffles
+    int red_floats;
+    int ntensors;  // 1 forward (x), 2 backward (x, dy)
 };
 
-// tile footprint in shared memory, padded so that a second tile stays 128-byte aligned
+// tile footprint in shared memory, padded so that the next tile stays 128-byte aligned
 __host__ __device__ static inline size_t gn_tile_bytes(const GnGeom& g)
 {
     return ((size_t)g.R * g.Ct * sizeof(float) + 127) & ~(size_t)127;
 }
 
-static inline size_t gn_smem_bytes(const GnGeom& g, int ntiles)
+static inline size_t gn_smem_bytes(const GnGeom& g)
 {
-    // tiles | reduction buffer | per-channel pair | per-group pair | barriers
-    return ntiles * gn_tile_bytes(g) + GN_RED_FLOATS * sizeof(float) + 2 * g.Ct * sizeof(float)
-        + 2 * g.Gt * sizeof(float) + GN_MAX_CHUNKS * sizeof(uint64_t) + 128;
+    // tiles | fold buffer | per-channel pairs (one per buffer) | per-group pair | barriers
+    return (size_t)GN_NBUF * g.ntensors * gn_tile_bytes(g) + (size_t)g.red_floats * sizeof(float)
+        + (size_t)GN_NBUF * 2 * g.Ct * sizeof(float) + 2 * g.Gt * sizeof(float)
+        + GN_NBUF * GN_MAX_CHUNKS * sizeof(uint64_t) + 128 + 16;
 }
 
 static int largest_divisor_leq(int n, int cap)
@@ -65,11 +77,12 @@ static int largest_divisor_leq(int n, int cap)
     return 1;
 }
 
-// Picks (Ct, CS).  ntiles = 1 (forward) or 2 (backward keeps x and dy).
-// Preference: tile set within `budget` bytes (so that several CTAs share an SM
-// and loads of one overlap stores of another), then rows of at least 128 bytes,
-// then the smallest cluster, then the widest tile.
-static bool gn_pick_geometry(GnGeom* out, int HW, int C, int G, int ntiles, int force_ct, int force_cs, size_t budget)
+// Picks (Ct, CS) and the persistent grid.
+// Preference: the double-buffered tile set within `budget` bytes (so that
+// `ctas_per_sm` CTAs share an SM), rows of at least 128 bytes, the smallest
+// cluster, then the widest tile.
+static bool gn_pick_geometry(GnGeom* out, int B, int HW, int C, int G, int ntensors, int force_ct, int force_cs,
+    size_t budget, int ctas_per_sm)
 {
     if (C % 4 != 0 || G <= 0 || C % G != 0)
         return false;
@@ -90,19 +103,24 @@ static bool gn_pick_geometry(GnGeom* out, int HW, int C, int G, int ntiles, int 
                 continue;
             if (force_cs > 0 && CS != force_cs)
                 continue;
-            GnGeom g;
+            GnGeom g = {};
             g.HW = HW; g.C = C; g.G = G; g.cpg = cpg;
             g.Ct = Ct; g.Q = Q; g.RSTEP = GN_THREADS / Q; g.CS = CS;
             g.R = HW / CS;
             g.RB = largest_divisor_leq(g.R, 256);
             g.nchunk = g.R / g.RB;
             g.Gt = Ct / cpg;
-            if (g.nchunk > GN_MAX_CHUNKS || (g.RB < 8 && g.R >= 8))
+            g.nct = C / Ct;
+            g.items = B * g.nct;
+            g.ntensors = ntensors;
+            g.shuffle = (Q <= 32 && 32 % Q == 0) ? 1 : 0;
+            g.red_floats = g.shuffle ? 2 * GN_WARPS * Ct : 2 * GN_THREADS * 4;
+            if (g.nchunk > GN_MAX_CHUNKS || (g.RB < 8 && g.R >= 8) || g.R < 2)
                 continue;
             // every chunk must start on a 128-byte boundary of shared memory
             if (g.nchunk > 1 && (g.RB * Ct) % 32 != 0)
                 continue;
-            const size_t bytes = ntiles * gn_tile_bytes(g);
+            const size_t bytes = (size_t)GN_NBUF * ntensors * gn_tile_bytes(g);
             if (bytes > hard_cap)
                 continue;
             long score = 0;
@@ -121,34 +139,54 @@ static bool gn_pick_geometry(GnGeom* out, int HW, int C, int G, int ntiles, int 
             }
         }
     }
-    return found;
+    if (!found)
+        return false;
+    // persistent grid: as many clusters as fit, then evened out so that every
+    // cluster gets (almost) the same number of items
+    GnGeom& g = *out;
+    const size_t smem = gn_smem_bytes(g);
+    int fit = (int)((size_t)227 * 1024 / (smem + 1024));
+    if (fit < 1)
+        fit = 1;
+    if (fit > ctas_per_sm)
+        fit = ctas_per_sm;
+    if (fit * GN_THREADS > 2048)
+        fit = 2048 / GN_THREADS;
+    int max_clusters = sm_count() * fit / g.CS;
+    if (max_clusters < 1)
+        max_clusters = 1;
+    if (g.items <= max_clusters) {
+        g.nclusters = g.items;
+    } else {
+        const int per = (g.items + max_clusters - 1) / max_clusters;
+        g.nclusters = (g.items + per - 1) / per;
+    }
+    return true;
 }
 
 // ---------------------------------------------------------------------------
 // shared pieces of the tile kernels
 // ---------------------------------------------------------------------------
 struct GnSmem {
-    float* tile0;
-    float* tile1;
-    float* red;     // GN_RED_FLOATS
-    float* chan;    // 2*Ct, read by cluster peers
+    float* tiles;   // [GN_NBUF][ntensors] tiles
+    float* red;     // red_floats
+    float* chan;    // [GN_NBUF][2*Ct], read by cluster peers
     float* gstat;   // 2*Gt
-    uint64_t* bars; // GN_MAX_CHUNKS
+    uint64_t* bars; // [GN_NBUF][GN_MAX_CHUNKS]
+    size_t tile_floats;
 };
 
-__device__ __forceinline__ GnSmem gn_carve(unsigned char* raw, const GnGeom& g, int ntiles)
+__device__ __forceinline__ GnSmem gn_carve(unsigned char* raw, const GnGeom& g)
 {
     GnSmem s;
     uintptr_t p = (reinterpret_cast<uintptr_t>(raw) + 127) & ~uintptr_t(127);
-    s.tile0 = reinterpret_cast<float*>(p);
-    p += gn_tile_bytes(g);
-    s.tile1 = reinterpret_cast<float*>(p);
-    if (ntiles == 2)
-        p += gn_tile_bytes(g);
+    s.tiles = reinterpret_cast<float*>(p);
+    s.tile_floats = gn_tile_bytes(g) / sizeof(float);
+    p += (size_t)GN_NBUF * g.ntensors * gn_tile_bytes(g);
     s.red = reinterpret_cast<float*>(p);
-    p += GN_RED_FLOATS * sizeof(float);
+    p += (size_t)g.red_floats * sizeof(float);
     s.chan = reinterpret_cast<float*>(p);
-    p += 2 * g.Ct * sizeof(float);
+    p += (size_t)GN_NBUF * 2 * g.Ct * sizeof(float);
     s.gstat = reinterpret_cast<float*>(p);
     p += 2 * g.Gt * sizeof(float);
     p = (p + 7) & ~uintptr_t(7);
@@ -156,154 +194,228 @@ __device__ __forceinline__ GnSmem gn_carve(unsigned char* raw, const GnGeom& g, 
     return s;
 }
 
-// Sums the per-thread float4 pairs (a, b) over the row lanes: afterwards
-// red[c] and red[Ct + c] hold the CTA totals of channel c for a and b.
-// Threads with rr >= RSTEP (idle lanes when Q does not divide the CTA) pass zeros.
-__device__ __forceinline__ void gn_fold_rows(float* red, const GnGeom& g, int q, int rr, bool active, float4 a, float4 b)
+__device__ __forceinline__ float* gn_tile(const GnSmem& s, const GnGeom& g, int buf, int tensor)
 {
-    float4* ra = reinterpret_cast<float4*>(red);
-    float4* rb = reinterpret_cast<float4*>(red + GN_THREADS * 4);
-    if (active) {
-        ra[rr * g.Q + q] = a;
-        rb[rr * g.Q + q] = b;
-    }
-    __syncthreads();
-    float sa = 0.0f, sb = 0.0f;
-    const int c = threadIdx.x;
-    if (c < g.Ct) {
-        for (int r = 0; r < g.RSTEP; ++r) {
-            sa += red[r * g.Ct + c];
-            sb += red[GN_THREADS * 4 + r * g.Ct + c];
+    return s.tiles + (size_t)(buf * g.ntensors + tensor) * s.tile_floats;
+}
+
+__device__ __forceinline__ float4 shfl_xor4(float4 v, int off)
+{
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+    v.z += __shfl_xor_sync(0xffffffffu, v.z, off);
+    v.w += __shfl_xor_sync(0xffffffffu, v.w, off);
+    return v;
+}
+
+// Sums the per-thread float4 pairs (a, b) over all row lanes of the CTA and
+// stores, for every channel c of the tile, the totals into dst[c] and
+// dst[Ct + c].  The caller synchronises before reading dst and before the next
+// use of `red`.
+__device__ __forceinline__ void gn_fold_rows(float* red, float* dst, const GnGeom& g, int q, int rr, bool active,
+    float4 a, float4 b)
+{
+    const int t = threadIdx.x;
+    if (g.shuffle) {
+        for (int off = g.Q; off < 32; off <<= 1) {
+            a = shfl_xor4(a, off);
+            b = shfl_xor4(b, off);
+        }
+        const int lane = t & 31, warp = t >> 5;
+        if (lane < g.Q) {
+            reinterpret_cast<float4*>(red)[warp * g.Q + lane] = a;
+            reinterpret_cast<float4*>(red + GN_WARPS * g.Ct)[warp * g.Q + lane] = b;
+        }
+        __syncthreads();
+        if (t < g.Ct) {
+            float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GN_WARPS; ++w) {
+                sa += red[w * g.Ct + t];
+                sb += red[GN_WARPS * g.Ct + w * g.Ct + t];
+            }
+            dst[t] = sa;
+            dst[g.Ct + t] = sb;
+        }
+    } else {
+        float4* ra = reinterpret_cast<float4*>(red);
+        float4* rb = reinterpret_cast<float4*>(red + GN_THREADS * 4);
+        if (active) {
+            ra[rr * g.Q + q] = a;
+            rb[rr * g.Q + q] = b;
+        }
+        __syncthreads();
+        if (t < g.Ct) {
+            float sa = 0.0f, sb = 0.0f;
+            for (int r = 0; r < g.RSTEP; ++r) {
+                sa += red[r * g.Ct + t];
+                sb += red[GN_THREADS * 4 + r * g.Ct + t];
+            }
+            dst[t] = sa;
+            dst[g.Ct + t] = sb;
         }
     }
-    __syncthreads();
-    if (c < g.Ct) {
-        red[c] = sa;
-        red[g.Ct + c] = sb;
+}
+
+// thread 0: (re)arm the barriers of buffer `buf` and start the loads of `item`
+__device__ __forceinline__ void gn_issue_loads(const GnSmem& sm, const GnGeom& g, int buf, int item, int rank,
+    const CUtensorMap* map0, const CUtensorMap* map1)
+{
+    const int ctile = item % g.nct, b = item / g.nct;
+    const int c0 = ctile * g.Ct;
+    const int row0 = b * g.HW + rank * g.R;
+    const unsigned chunk_bytes = (unsigned)(g.RB * g.Ct * sizeof(float));
+    for (int c = 0; c < g.nchunk; ++c) {
+        uint64_t* bar = &sm.bars[buf * GN_MAX_CHUNKS + c];
+        mbar_expect_tx(bar, chunk_bytes * g.ntensors);
+        tma_load_2d(gn_tile(sm, g, buf, 0) + (size_t)c * g.RB * g.Ct, map0, c0, row0 + c * g.RB, bar);
+        if (g.ntensors == 2)
+            tma_load_2d(gn_tile(sm, g, buf, 1) + (size_t)c * g.RB * g.Ct, map1, c0, row0 + c * g.RB, bar);
     }
-    __syncthreads();
+}
+
+// Warp-parallel combine of the per-channel (mean, centred sum of squares) pairs of
+// all CTAs of the cluster into group statistics (Chan et al. pairwise update with
+// equal counts).  Warp w handles groups w, w+GN_WARPS, ...
+__device__ __forceinline__ void gn_group_stats(cg::cluster_group& cluster, const GnSmem& sm, const GnGeom& g,
+    float* chan, int rank, int group0, float eps, float* __restrict__ mu, float* __restrict__ rstd, int b)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nparts = g.CS * g.cpg;
+    for (int grp = warp; grp < g.Gt; grp += GN_WARPS) {
+        float msum = 0.0f;
+        for (int e = lane; e < nparts; e += 32) {
+            const float* peer = cluster.map_shared_rank(chan, e / g.cpg);
+            msum += peer[grp * g.cpg + e % g.cpg];
+        }
+        const float mean = warp_sum(msum) / (float)nparts;
+        float m2 = 0.0f;
+        for (int e = lane; e < nparts; e += 32) {
+            const float* peer = cluster.map_shared_rank(chan, e / g.cpg);
+            const int ch = grp * g.cpg + e % g.cpg;
+            const float d = peer[ch] - mean;
+            m2 += peer[g.Ct + ch] + (float)g.R * d * d;
+        }
+        m2 = warp_sum(m2);
+        const float rs = rsqrtf(m2 / ((float)g.R * (float)nparts) + eps);
+        if (lane == 0) {
+            sm.gstat[grp] = mean;
+            sm.gstat[g.Gt + grp] = rs;
+            if (rank == 0) {
+                mu[b * g.G + group0 + grp] = mean;
+                rstd[b * g.G + group0 + grp] = rs;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
 template <int ACT>
-__global__ void __launch_bounds__(GN_THREADS) gn_fwd_tile(const __grid_constant__ CUtensorMap map_x,
+__global__ void __launch_bounds__(GN_THREADS, 2) gn_fwd_tile(const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_y, float* __restrict__ mu, float* __restrict__ rstd,
     const float* __restrict__ gamma, const float* __restrict__ beta, const GnGeom g, const float eps, int* err)
 {
     extern __shared__ unsigned char gn_smem_raw[];
     cg::cluster_group cluster = cg::this_cluster();
-    const GnSmem sm = gn_carve(gn_smem_raw, g, 1);
+    const GnSmem sm = gn_carve(gn_smem_raw, g);
     const int t = threadIdx.x;
-    const int rank = blockIdx.x;  // cluster spans gridDim.x
-    const int c0 = blockIdx.y * g.Ct;
-    const int b = blockIdx.z;
-    const int row0 = b * g.HW + rank * g.R;
+    const int rank = (int)cluster.block_rank();
+    const int cluster_id = blockIdx.x / g.CS;
     const int q = t % g.Q, rr = t / g.Q;
     const bool active = rr < g.RSTEP;
-    const unsigned chunk_bytes = (unsigned)(g.RB * g.Ct * sizeof(float));
 
     if (t == 0) {
-        for (int c = 0; c < g.nchunk; ++c)
-            mbar_init(&sm.bars[c], 1);
+        for (int i = 0; i < GN_NBUF * GN_MAX_CHUNKS; ++i)
+            mbar_init(&sm.bars[i], 1);
         mbar_init_fence();
+        gn_issue_loads(sm, g, 0, cluster_id, rank, &map_x, nullptr);
+    }
+    __syncthreads();
+
+    int it = 0;
+    for (int item = cluster_id; item < g.items; item += g.nclusters, ++it) {
+        const int buf = it & 1;
+        const unsigned parity = (unsigned)(it >> 1) & 1u;
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const int row0 = b * g.HW + rank * g.R;
+        // prefetch the next item into the other buffer once its stores have drained
+        if (t == 0 && item + g.nclusters < g.items) {
+            tma_store_wait_read();
+            gn_issue_loads(sm, g, buf ^ 1, item + g.nclusters, rank, &map_x, nullptr);
+        }
+        float* tile = gn_tile(sm, g, buf, 0);
+        float* chan = sm.chan + (size_t)buf * 2 * g.Ct;
+
+        // ---- statistics, shifted by row 0 of the tile (K) so that the one-pass
+        //      sums of (x-K) and (x-K)^2 do not cancel
+        const float4* tile4 = reinterpret_cast<const float4*>(tile);
+        float4 K = make_float4(0.f, 0.f, 0.f, 0.f), s1 = K, s2 = K;
         for (int c = 0; c < g.nchunk; ++c) {
-            mbar_expect_tx(&sm.bars[c], chunk_bytes);
-            tma_load_2d(sm.tile0 + (size_t)c * g.RB * g.Ct, &map_x, c0, row0 + c * g.RB, &sm.bars[c]);
-        }
-    }
-    __syncthreads();
-
-    // ---- statistics, shifted by row 0 of the tile (K) so that the one-pass
-    //      sums of (x-K) and (x-K)^2 do not cancel
-    const float4* tile4 = reinterpret_cast<const float4*>(sm.tile0);
-    float4 K = make_float4(0.f, 0.f, 0.f, 0.f), s1 = K, s2 = K;
-    for (int c = 0; c < g.nchunk; ++c) {
-        mbar_wait(&sm.bars[c], 0, err);
-        if (c == 0 && active)
-            K = tile4[q];
-        if (active) {
-            for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
-                const float4 v = tile4[(size_t)(c * g.RB + lr) * g.Q + q];
-                const float d0 = v.x - K.x, d1 = v.y - K.y, d2 = v.z - K.z, d3 = v.w - K.w;
-                s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
-                s2.x += d0 * d0; s2.y += d1 * d1; s2.z += d2 * d2; s2.w += d3 * d3;
+            mbar_wait(&sm.bars[buf * GN_MAX_CHUNKS + c], parity, err);
+            if (active) {
+                if (c == 0)
+                    K = tile4[q];
+                for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
+                    const float4 v = tile4[(size_t)(c * g.RB + lr) * g.Q + q];
+                    const float d0 = v.x - K.x, d1 = v.y - K.y, d2 = v.z - K.z, d3 = v.w - K.w;
+                    s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
+                    s2.x += d0 * d0; s2.y += d1 * d1; s2.z += d2 * d2; s2.w += d3 * d3;
+                }
             }
         }
-    }
-    gn_fold_rows(sm.red, g, q, rr, active, s1, s2);
-    if (t < g.Ct) {
-        const float invR = 1.0f / (float)g.R;
-        const float S1 = sm.red[t], S2 = sm.red[g.Ct + t];
-        sm.chan[t] = sm.tile0[t] + S1 * invR;          // channel mean over this CTA's rows
-        sm.chan[g.Ct + t] = S2 - S1 * S1 * invR;       // centred sum of squares
-    }
-    cluster.sync();
-
-    // ---- combine channels of a group and the CTAs of the cluster (Chan et al.)
-    if (t < g.Gt) {
-        const int nparts = g.CS * g.cpg;
-        float msum = 0.0f;
-        for (int k = 0; k < g.CS; ++k) {
-            const float* peer = cluster.map_shared_rank(sm.chan, k);
-            for (int cl = 0; cl < g.cpg; ++cl)
-                msum += peer[t * g.cpg + cl];
+        gn_fold_rows(sm.red, chan, g, q, rr, active, s1, s2);
+        if (t < g.Ct) {
+            const float invR = 1.0f / (float)g.R;
+            const float S1 = chan[t], S2 = chan[g.Ct + t];
+            chan[t] = tile[t] + S1 * invR;          // channel mean over this CTA's rows
+            chan[g.Ct + t] = S2 - S1 * S1 * invR;   // centred sum of squares
         }
-        const float mean = msum / (float)nparts;
-        float m2 = 0.0f;
-        for (int k = 0; k < g.CS; ++k) {
-            const float* peer = cluster.map_shared_rank(sm.chan, k);
-            for (int cl = 0; cl < g.cpg; ++cl) {
-                const float d = peer[t * g.cpg + cl] - mean;
-                m2 += peer[g.Ct + t * g.cpg + cl] + (float)g.R * d * d;
-            }
-        }
-        const float var = m2 / ((float)g.R * (float)nparts);
-        const float rs = rsqrtf(var + eps);
-        sm.gstat[t] = mean;
-        sm.gstat[g.Gt + t] = rs;
-        if (rank == 0) {
-            mu[b * g.G + c0 / g.cpg + t] = mean;
-            rstd[b * g.G + c0 / g.cpg + t] = rs;
-        }
-    }
-    __syncthreads();
-
-    // ---- normalise + affine (+ activation) in place, store chunk by chunk
-    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), be = ga, mean4 = ga, rs4 = ga;
-    if (active) {
-        ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
-        be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
-        const int cb = 4 * q;
-        mean4.x = sm.gstat[(cb + 0) / g.cpg]; rs4.x = sm.gstat[g.Gt + (cb + 0) / g.cpg];
-        mean4.y = sm.gstat[(cb + 1) / g.cpg]; rs4.y = sm.gstat[g.Gt + (cb + 1) / g.cpg];
-        mean4.z = sm.gstat[(cb + 2) / g.cpg]; rs4.z = sm.gstat[g.Gt + (cb + 2) / g.cpg];
-        mean4.w = sm.gstat[(cb + 3) / g.cpg]; rs4.w = sm.gstat[g.Gt + (cb + 3) / g.cpg];
-    }
-    float4* wtile4 = reinterpret_cast<float4*>(sm.tile0);
-    for (int c = 0; c < g.nchunk; ++c) {
-        if (active) {
-            for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
-                float4* p = wtile4 + (size_t)(c * g.RB + lr) * g.Q + q;
-                float4 v = *p;
-                v.x = act_value<ACT>(ga.x * ((v.x - mean4.x) * rs4.x) + be.x);
-                v.y = act_value<ACT>(ga.y * ((v.y - mean4.y) * rs4.y) + be.y);
-                v.z = act_value<ACT>(ga.z * ((v.z - mean4.z) * rs4.z) + be.z);
-                v.w = act_value<ACT>(ga.w * ((v.w - mean4.w) * rs4.w) + be.w);
-                *p = v;
-            }
-        }
-        fence_async_smem();
+        if (g.CS > 1)
+            cluster.sync();
+        else
+            __syncthreads();
+        gn_group_stats(cluster, sm, g, chan, rank, c0 / g.cpg, eps, mu, rstd, b);
         __syncthreads();
-        if (t == 0) {
-            tma_store_2d(&map_y, sm.tile0 + (size_t)c * g.RB * g.Ct, c0, row0 + c * g.RB);
-            tma_store_commit();
+
+        // ---- y = act(x*a + b') with a = gamma*rstd, b' = beta - mean*a; in place, then TMA store
+        float4 sc = make_float4(0.f, 0.f, 0.f, 0.f), sh = sc;
+        if (active) {
+            const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+            const float4 be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+            const int cb = 4 * q;
+            const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
+            sc.x = ga.x * sm.gstat[g.Gt + g0]; sh.x = be.x - sm.gstat[g0] * sc.x;
+            sc.y = ga.y * sm.gstat[g.Gt + g1]; sh.y = be.y - sm.gstat[g1] * sc.y;
+            sc.z = ga.z * sm.gstat[g.Gt + g2]; sh.z = be.z - sm.gstat[g2] * sc.z;
+            sc.w = ga.w * sm.gstat[g.Gt + g3]; sh.w = be.w - sm.gstat[g3] * sc.w;
+        }
+        float4* wtile4 = reinterpret_cast<float4*>(tile);
+        for (int c = 0; c < g.nchunk; ++c) {
+            if (active) {
+                for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
+                    float4* p = wtile4 + (size_t)(c * g.RB + lr) * g.Q + q;
+                    float4 v = *p;
+                    v.x = act_value<ACT>(fmaf(v.x, sc.x, sh.x));
+                    v.y = act_value<ACT>(fmaf(v.y, sc.y, sh.y));
+                    v.z = act_value<ACT>(fmaf(v.z, sc.z, sh.z));
+                    v.w = act_value<ACT>(fmaf(v.w, sc.w, sh.w));
+                    *p = v;
+                }
+            }
+            fence_async_smem();
+            __syncthreads();
+            if (t == 0) {
+                tma_store_2d(&map_y, tile + (size_t)c * g.RB * g.Ct, c0, row0 + c * g.RB);
+                tma_store_commit();
+            }
         }
     }
     if (t == 0)
         tma_store_wait_read();
-    cluster.sync();  // peers may still be reading this CTA's per-channel pair
+    cluster.sync();  // peers may still be reading this CTA's per-channel pairs
 }
 
 // ---------------------------------------------------------------------------
@@ -311,7 +423,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_fwd_tile(const __grid_constant_
 // ---------------------------------------------------------------------------
 // partials layout: [C/Ct tiles][B samples][2*Ct]  (first Ct: dgamma, next Ct: dbeta)
 template <int ACT>
-__global__ void __launch_bounds__(GN_THREADS) gn_bwd_tile(const __grid_constant__ CUtensorMap map_x,
+__global__ void __launch_bounds__(GN_THREADS, 2) gn_bwd_tile(const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_dx,
     float* __restrict__ partials, unsigned int* __restrict__ tickets, float* __restrict__ dgamma,
     float* __restrict__ dbeta, const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -320,172 +432,190 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_tile(const __grid_constant_
     extern __shared__ unsigned char gn_smem_raw[];
     __shared__ int s_is_last;
     cg::cluster_group cluster = cg::this_cluster();
-    const GnSmem sm = gn_carve(gn_smem_raw, g, 2);
+    const GnSmem sm = gn_carve(gn_smem_raw, g);
     const int t = threadIdx.x;
-    const int rank = blockIdx.x;
-    const int c0 = blockIdx.y * g.Ct;
-    const int b = blockIdx.z;
-    const int row0 = b * g.HW + rank * g.R;
+    const int lane = t & 31, warp = t >> 5;
+    const int rank = (int)cluster.block_rank();
+    const int cluster_id = blockIdx.x / g.CS;
     const int q = t % g.Q, rr = t / g.Q;
     const bool active = rr < g.RSTEP;
-    const unsigned chunk_bytes = (unsigned)(g.RB * g.Ct * sizeof(float));
+    const int cb = 4 * q;
+    const int gl0 = (cb + 0) / g.cpg, gl1 = (cb + 1) / g.cpg, gl2 = (cb + 2) / g.cpg, gl3 = (cb + 3) / g.cpg;
 
     if (t == 0) {
-        for (int c = 0; c < g.nchunk; ++c)
-            mbar_init(&sm.bars[c], 1);
+        for (int i = 0; i < GN_NBUF * GN_MAX_CHUNKS; ++i)
+            mbar_init(&sm.bars[i], 1);
         mbar_init_fence();
-        for (int c = 0; c < g.nchunk; ++c) {
-            mbar_expect_tx(&sm.bars[c], 2 * chunk_bytes);
-            tma_load_2d(sm.tile0 + (size_t)c * g.RB * g.Ct, &map_x, c0, row0 + c * g.RB, &sm.bars[c]);
-            tma_load_2d(sm.tile1 + (size_t)c * g.RB * g.Ct, &map_dy, c0, row0 + c * g.RB, &sm.bars[c]);
-        }
-    }
-
-    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), be = ga, mean4 = ga, rs4 = ga;
-    int gl0 = 0, gl1 = 0, gl2 = 0, gl3 = 0;  // tile-local group of each of the 4 lanes
-    if (active) {
-        ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
-        if (ACT != ACT_IDENTITY)
-            be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
-        const int cb = 4 * q;
-        gl0 = (cb + 0) / g.cpg; gl1 = (cb + 1) / g.cpg; gl2 = (cb + 2) / g.cpg; gl3 = (cb + 3) / g.cpg;
-        const int gbase = b * g.G + c0 / g.cpg;
-        mean4.x = __ldg(mu + gbase + gl0); rs4.x = __ldg(rstd + gbase + gl0);
-        mean4.y = __ldg(mu + gbase + gl1); rs4.y = __ldg(rstd + gbase + gl1);
-        mean4.z = __ldg(mu + gbase + gl2); rs4.z = __ldg(rstd + gbase + gl2);
-        mean4.w = __ldg(mu + gbase + gl3); rs4.w = __ldg(rstd + gbase + gl3);
+        gn_issue_loads(sm, g, 0, cluster_id, rank, &map_x, &map_dy);
     }
     __syncthreads();
 
-    // ---- pass 1: xhat and the effective upstream gradient replace x and dy in
-    //      shared memory; per-channel sums of dy and dy*xhat
-    float4* xt4 = reinterpret_cast<float4*>(sm.tile0);
-    float4* gt4 = reinterpret_cast<float4*>(sm.tile1);
-    float4 sA = make_float4(0.f, 0.f, 0.f, 0.f), sB = sA;
-    for (int c = 0; c < g.nchunk; ++c) {
-        mbar_wait(&sm.bars[c], 0, err);
+    int it = 0;
+    for (int item = cluster_id; item < g.items; item += g.nclusters, ++it) {
+        const int buf = it & 1;
+        const unsigned parity = (unsigned)(it >> 1) & 1u;
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const int row0 = b * g.HW + rank * g.R;
+        if (t == 0 && item + g.nclusters < g.items) {
+            tma_store_wait_read();
+            gn_issue_loads(sm, g, buf ^ 1, item + g.nclusters, rank, &map_x, &map_dy);
+        }
+        float* chan = sm.chan + (size_t)buf * 2 * g.Ct;
+        float4* xt4 = reinterpret_cast<float4*>(gn_tile(sm, g, buf, 0));
+        float4* gt4 = reinterpret_cast<float4*>(gn_tile(sm, g, buf, 1));
+
+        float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), be = ga, rs4 = ga, nm4 = ga;
         if (active) {
-            for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
-                const size_t idx = (size_t)(c * g.RB + lr) * g.Q + q;
-                float4 xv = xt4[idx], dv = gt4[idx];
-                xv.x = (xv.x - mean4.x) * rs4.x;
-                xv.y = (xv.y - mean4.y) * rs4.y;
-                xv.z = (xv.z - mean4.z) * rs4.z;
-                xv.w = (xv.w - mean4.w) * rs4.w;
-                if (ACT != ACT_IDENTITY) {
-                    dv.x *= act_slope<ACT>(ga.x * xv.x + be.x);
-                    dv.y *= act_slope<ACT>(ga.y * xv.y + be.y);
-                    dv.z *= act_slope<ACT>(ga.z * xv.z + be.z);
-                    dv.w *= act_slope<ACT>(ga.w * xv.w + be.w);
+            ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+            if (ACT != ACT_IDENTITY)
+                be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+            const int gbase = b * g.G + c0 / g.cpg;
+            rs4.x = __ldg(rstd + gbase + gl0); nm4.x = -__ldg(mu + gbase + gl0) * rs4.x;
+            rs4.y = __ldg(rstd + gbase + gl1); nm4.y = -__ldg(mu + gbase + gl1) * rs4.y;
+            rs4.z = __ldg(rstd + gbase + gl2); nm4.z = -__ldg(mu + gbase + gl2) * rs4.z;
+            rs4.w = __ldg(rstd + gbase + gl3); nm4.w = -__ldg(mu + gbase + gl3) * rs4.w;
+        }
+
+        // ---- pass 1: xhat and the effective upstream gradient replace x and dy in
+        //      shared memory; per-channel sums of dy and dy*xhat
+        float4 sA = make_float4(0.f, 0.f, 0.f, 0.f), sB = sA;
+        for (int c = 0; c < g.nchunk; ++c) {
+            mbar_wait(&sm.bars[buf * GN_MAX_CHUNKS + c], parity, err);
+            if (active) {
+                for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
+                    const size_t idx = (size_t)(c * g.RB + lr) * g.Q + q;
+                    float4 xv = xt4[idx], dv = gt4[idx];
+                    xv.x = fmaf(xv.x, rs4.x, nm4.x);
+                    xv.y = fmaf(xv.y, rs4.y, nm4.y);
+                    xv.z = fmaf(xv.z, rs4.z, nm4.z);
+                    xv.w = fmaf(xv.w, rs4.w, nm4.w);
+                    if (ACT != ACT_IDENTITY) {
+                        dv.x *= act_slope<ACT>(fmaf(ga.x, xv.x, be.x));
+                        dv.y *= act_slope<ACT>(fmaf(ga.y, xv.y, be.y));
+                        dv.z *= act_slope<ACT>(fmaf(ga.z, xv.z, be.z));
+                        dv.w *= act_slope<ACT>(fmaf(ga.w, xv.w, be.w));
+                        gt4[idx] = dv;
+                    }
+                    xt4[idx] = xv;
+                    sA.x += dv.x; sA.y += dv.y; sA.z += dv.z; sA.w += dv.w;
+                    sB.x = fmaf(dv.x, xv.x, sB.x); sB.y = fmaf(dv.y, xv.y, sB.y);
+                    sB.z = fmaf(dv.z, xv.z, sB.z); sB.w = fmaf(dv.w, xv.w, sB.w);
+                }
+            }
+        }
+        // chan[c] = sum_rows dy (-> dbeta), chan[Ct+c] = sum_rows dy*xhat (-> dgamma)
+        gn_fold_rows(sm.red, chan, g, q, rr, active, sA, sB);
+        if (g.CS > 1)
+            cluster.sync();
+        else
+            __syncthreads();
+
+        // ---- group sums over the cluster (one warp per group); sample partials
+        {
+            const int nparts = g.CS * g.cpg;
+            const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
+            for (int grp = warp; grp < g.Gt; grp += GN_WARPS) {
+                float sg = 0.0f, sgx = 0.0f;
+                for (int e = lane; e < nparts; e += 32) {
+                    const float* peer = cluster.map_shared_rank(chan, e / g.cpg);
+                    const int ch = grp * g.cpg + e % g.cpg;
+                    const float gm = __ldg(gamma + c0 + ch);
+                    sg = fmaf(gm, peer[ch], sg);
+                    sgx = fmaf(gm, peer[g.Ct + ch], sgx);
+                }
+                sg = warp_sum(sg);
+                sgx = warp_sum(sgx);
+                if (lane == 0) {
+                    sm.gstat[grp] = sg * inv_n;
+                    sm.gstat[g.Gt + grp] = sgx * inv_n;
+                }
+            }
+            if (rank == 0 && t < g.Ct) {
+                float a = 0.0f, bsum = 0.0f;
+                for (int k = 0; k < g.CS; ++k) {
+                    const float* peer = cluster.map_shared_rank(chan, k);
+                    a += peer[t];
+                    bsum += peer[g.Ct + t];
+                }
+                float* dst = partials + ((size_t)ctile * B + b) * (2 * g.Ct);
+                dst[t] = bsum;
+                dst[g.Ct + t] = a;
+            }
+        }
+        __syncthreads();
+
+        // ---- pass 2: dx = rstd * (gamma*dy - mean(gamma*dy) - xhat * mean(gamma*dy*xhat))
+        float4 mg = make_float4(0.f, 0.f, 0.f, 0.f), mgx = mg;
+        if (active) {
+            mg.x = sm.gstat[gl0]; mgx.x = sm.gstat[g.Gt + gl0];
+            mg.y = sm.gstat[gl1]; mgx.y = sm.gstat[g.Gt + gl1];
+            mg.z = sm.gstat[gl2]; mgx.z = sm.gstat[g.Gt + gl2];
+            mg.w = sm.gstat[gl3]; mgx.w = sm.gstat[g.Gt + gl3];
+        }
+        for (int c = 0; c < g.nchunk; ++c) {
+            if (active) {
+                for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
+                    const size_t idx = (size_t)(c * g.RB + lr) * g.Q + q;
+                    const float4 xv = xt4[idx];
+                    float4 dv = gt4[idx];
+                    dv.x = rs4.x * (fmaf(dv.x, ga.x, -mg.x) - xv.x * mgx.x);
+                    dv.y = rs4.y * (fmaf(dv.y, ga.y, -mg.y) - xv.y * mgx.y);
+                    dv.z = rs4.z * (fmaf(dv.z, ga.z, -mg.z) - xv.z * mgx.z);
+                    dv.w = rs4.w * (fmaf(dv.w, ga.w, -mg.w) - xv.w * mgx.w);
                     gt4[idx] = dv;
                 }
-                xt4[idx] = xv;
-                sA.x += dv.x; sA.y += dv.y; sA.z += dv.z; sA.w += dv.w;
-                sB.x += dv.x * xv.x; sB.y += dv.y * xv.y; sB.z += dv.z * xv.z; sB.w += dv.w * xv.w;
+            }
+            fence_async_smem();
+            __syncthreads();
+            if (t == 0) {
+                tma_store_2d(&map_dx, gn_tile(sm, g, buf, 1) + (size_t)c * g.RB * g.Ct, c0, row0 + c * g.RB);
+                tma_store_commit();
             }
         }
-    }
-    gn_fold_rows(sm.red, g, q, rr, active, sA, sB);
-    if (t < g.Ct) {
-        sm.chan[t] = sm.red[t];                // sum_rows dy          (-> dbeta)
-        sm.chan[g.Ct + t] = sm.red[g.Ct + t];  // sum_rows dy * xhat   (-> dgamma)
-    }
-    cluster.sync();
 
-    // ---- group sums over the cluster; sample partials for dgamma/dbeta
-    if (t < g.Gt) {
-        float sg = 0.0f, sgx = 0.0f;
-        for (int k = 0; k < g.CS; ++k) {
-            const float* peer = cluster.map_shared_rank(sm.chan, k);
-            for (int cl = 0; cl < g.cpg; ++cl) {
-                const int ch = t * g.cpg + cl;
-                const float gm = __ldg(gamma + c0 + ch);
-                sg += gm * peer[ch];
-                sgx += gm * peer[g.Ct + ch];
-            }
-        }
-        const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
-        sm.gstat[t] = sg * inv_n;
-        sm.gstat[g.Gt + t] = sgx * inv_n;
-    }
-    if (rank == 0 && t < g.Ct) {
-        float a = 0.0f, bsum = 0.0f;
-        for (int k = 0; k < g.CS; ++k) {
-            const float* peer = cluster.map_shared_rank(sm.chan, k);
-            a += peer[t];
-            bsum += peer[g.Ct + t];
-        }
-        float* dst = partials + ((size_t)blockIdx.y * B + b) * (2 * g.Ct);
-        dst[t] = bsum;
-        dst[g.Ct + t] = a;
-    }
-    __syncthreads();
-
-    // ---- pass 2: dx = rstd * (gamma*dy - mean(gamma*dy) - xhat * mean(gamma*dy*xhat))
-    float4 mg = make_float4(0.f, 0.f, 0.f, 0.f), mgx = mg;
-    if (active) {
-        mg.x = sm.gstat[gl0]; mgx.x = sm.gstat[g.Gt + gl0];
-        mg.y = sm.gstat[gl1]; mgx.y = sm.gstat[g.Gt + gl1];
-        mg.z = sm.gstat[gl2]; mgx.z = sm.gstat[g.Gt + gl2];
-        mg.w = sm.gstat[gl3]; mgx.w = sm.gstat[g.Gt + gl3];
-    }
-    for (int c = 0; c < g.nchunk; ++c) {
-        if (active) {
-            for (int lr = rr; lr < g.RB; lr += g.RSTEP) {
-                const size_t idx = (size_t)(c * g.RB + lr) * g.Q + q;
-                const float4 xv = xt4[idx];
-                float4 dv = gt4[idx];
-                dv.x = rs4.x * (dv.x * ga.x - mg.x - xv.x * mgx.x);
-                dv.y = rs4.y * (dv.y * ga.y - mg.y - xv.y * mgx.y);
-                dv.z = rs4.z * (dv.z * ga.z - mg.z - xv.z * mgx.z);
-                dv.w = rs4.w * (dv.w * ga.w - mg.w - xv.w * mgx.w);
-                gt4[idx] = dv;
-            }
-        }
-        fence_async_smem();
-        __syncthreads();
-        if (t == 0) {
-            tma_store_2d(&map_dx, sm.tile1 + (size_t)c * g.RB * g.Ct, c0, row0 + c * g.RB);
-            tma_store_commit();
-        }
-    }
-
-    // ---- the last sample to finish a channel tile adds the B partial rows
-    if (rank == 0) {
-        __threadfence();
-        __syncthreads();
-        if (t == 0) {
-            const unsigned old = atomicAdd(&tickets[blockIdx.y], 1u);
-            s_is_last = (old == (unsigned)B - 1u);
-        }
-        __syncthreads();
-        if (s_is_last) {
+        // ---- the last sample to finish a channel tile adds the B partial rows
+        if (rank == 0) {
             __threadfence();
-            const int width = 2 * g.Ct;
-            const int nq = width / 4;                 // float4 columns of a partial row
-            const int blanes = GN_THREADS / nq;       // samples summed concurrently
-            const int qi = t % nq, bl = t / nq;
-            const float* src = partials + (size_t)blockIdx.y * B * width;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (bl < blanes) {
-                for (int bb = bl; bb < B; bb += blanes) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
-                reinterpret_cast<float4*>(sm.red)[bl * nq + qi] = acc;
+            __syncthreads();
+            if (t == 0) {
+                const unsigned old = atomicAdd(&tickets[ctile], 1u);
+                s_is_last = (old == (unsigned)B - 1u);
             }
             __syncthreads();
-            for (int j = t; j < width; j += GN_THREADS) {
-                float s = 0.0f;
-                for (int r = 0; r < blanes; ++r)
-                    s += sm.red[r * width + j];
-                if (j < g.Ct)
-                    dgamma[c0 + j] = s;
-                else
-                    dbeta[c0 + j - g.Ct] = s;
+            if (s_is_last) {
+                __threadfence();
+                const int width = 2 * g.Ct;
+                const int nq = width / 4;                 // float4 columns of a partial row
+                const int blanes = GN_THREADS / nq;       // samples summed concurrently
+                const int qi = t % nq, bl = t / nq;
+                const float* src = partials + (size_t)ctile * B * width;
+                // sm.red may be too small for blanes*width floats: reuse the x tile of this buffer
+                float* fold = gn_tile(sm, g, buf, 0);
+                const int cap = (int)(sm.tile_floats / width);
+                const int lanes = blanes < cap ? blanes : cap;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (bl < lanes) {
+                    for (int bb = bl; bb < B; bb += lanes) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    reinterpret_cast<float4*>(fold)[bl * nq + qi] = acc;
+                }
+                __syncthreads();
+                for (int j = t; j < width; j += GN_THREADS) {
+                    float s = 0.0f;
+                    for (int r = 0; r < lanes; ++r)
+                        s += fold[r * width + j];
+                    if (j < g.Ct)
+                        dgamma[c0 + j] = s;
+                    else
+                        dbeta[c0 + j - g.Ct] = s;
+                }
+                if (t == 0)
+                    tickets[ctile] = 0;  // ready for the next launch
+                __syncthreads();
             }
-            if (t == 0)
-                tickets[blockIdx.y] = 0;  // ready for the next launch
         }
     }
     if (t == 0)
@@ -493,12 +623,18 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_tile(const __grid_constant_
     cluster.sync();
 }
 
+}  // namespace b200
+
+#include "groupnorm_strip.cuh"
+
+namespace b200 {
+
 // ---------------------------------------------------------------------------
 // generic kernels: one CTA per (sample, group), any C / HW / alignment.
 // The group is re-read from L2 for the second and third sweep.
 // ---------------------------------------------------------------------------
 template <int ACT>
-__global__ void __launch_bounds__(GN_THREADS) gn_fwd_generic(float* __restrict__ y, float* __restrict__ mu,
+__global__ void __launch_bounds__(GN_GENERIC_THREADS) gn_fwd_generic(float* __restrict__ y, float* __restrict__ mu,
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, int HW, int C, int G, float eps)
 {
@@ -507,11 +643,11 @@ __global__ void __launch_bounds__(GN_THREADS) gn_fwd_generic(float* __restrict__
     const int cpg = C / G, n = HW * cpg, cbase = grp * cpg;
     const float* xb = x + (size_t)b * HW * C;
     float s = 0.0f;
-    for (int i = threadIdx.x; i < n; i += GN_THREADS)
+    for (int i = threadIdx.x; i < n; i += GN_GENERIC_THREADS)
         s += xb[(size_t)(i / cpg) * C + cbase + i % cpg];
     const float mean = cta_sum(s, buf) / (float)n;
     float vs = 0.0f;
-    for (int i = threadIdx.x; i < n; i += GN_THREADS) {
+    for (int i = threadIdx.x; i < n; i += GN_GENERIC_THREADS) {
         const float d = xb[(size_t)(i / cpg) * C + cbase + i % cpg] - mean;
         vs += d * d;
     }
@@ -521,7 +657,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_fwd_generic(float* __restrict__
         rstd[blockIdx.x] = rs;
     }
     float* yb = y + (size_t)b * HW * C;
-    for (int i = threadIdx.x; i < n; i += GN_THREADS) {
+    for (int i = threadIdx.x; i < n; i += GN_GENERIC_THREADS) {
         const int cl = i % cpg;
         const size_t off = (size_t)(i / cpg) * C + cbase + cl;
         yb[off] = act_value<ACT>(gamma[cbase + cl] * ((xb[off] - mean) * rs) + beta[cbase + cl]);
@@ -537,7 +673,7 @@ __device__ __forceinline__ float gn_effective_grad(float dyv, float xhat, float 
 }
 
 template <int ACT>
-__global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_generic(float* __restrict__ dx, const float* __restrict__ dy,
+__global__ void __launch_bounds__(GN_GENERIC_THREADS) gn_bwd_dx_generic(float* __restrict__ dx, const float* __restrict__ dy,
     const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
     const float* __restrict__ mu, const float* __restrict__ rstd, int HW, int C, int G)
 {
@@ -547,7 +683,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_generic(float* __restric
     const size_t sample = (size_t)b * HW * C;
     const float mean = mu[blockIdx.x], rs = rstd[blockIdx.x];
     float pg = 0.0f, pgx = 0.0f;
-    for (int i = threadIdx.x; i < n; i += GN_THREADS) {
+    for (int i = threadIdx.x; i < n; i += GN_GENERIC_THREADS) {
         const int cl = i % cpg;
         const size_t off = sample + (size_t)(i / cpg) * C + cbase + cl;
         const float xh = (x[off] - mean) * rs;
@@ -559,7 +695,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_generic(float* __restric
     const float inv_n = 1.0f / (float)n;
     const float sg = cta_sum(pg, buf) * inv_n;
     const float sgx = cta_sum(pgx, buf) * inv_n;
-    for (int i = threadIdx.x; i < n; i += GN_THREADS) {
+    for (int i = threadIdx.x; i < n; i += GN_GENERIC_THREADS) {
         const int cl = i % cpg;
         const size_t off = sample + (size_t)(i / cpg) * C + cbase + cl;
         const float xh = (x[off] - mean) * rs;
@@ -631,7 +767,8 @@ static bool gn_allow_big_smem(K kernel, bool* done_for_device)
 static void gn_fill_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, const GnGeom& g, int B, size_t smem,
     cudaStream_t s)
 {
-    cfg->gridDim = dim3((unsigned)g.CS, (unsigned)(g.C / g.Ct), (unsigned)B);
+    (void)B;
+    cfg->gridDim = dim3((unsigned)(g.CS * g.nclusters), 1, 1);
     cfg->blockDim = dim3(GN_THREADS, 1, 1);
     cfg->dynamicSmemBytes = smem;
     cfg->stream = s;
@@ -645,7 +782,7 @@ static void gn_fill_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, c
 
 static bool gn_tile_shape_ok(int B, int HW, int C)
 {
-    return B > 0 && B <= 65535 && (long)B * HW < 2147483647L && (long)B * HW * C < 2147483648L && C % 4 == 0;
+    return B > 0 && (long)B * HW < 2147483647L && (long)B * HW * C < 2147483648L && C % 4 == 0;
 }
 
 // returns true if the tile kernel was launched
@@ -654,15 +791,16 @@ static bool gn_forward_tile(float* y, float* mu, float* rstd, const float* x, co
     const float* beta, int B, int HW, int C, int G, float eps, cudaStream_t s)
 {
     static bool smem_ok[64] = { false };
-    if (tune_get("gn_force_generic", 0) || !gn_tile_shape_ok(B, HW, C))
+    if (tune_get("gn_force_generic", 0) || tune_get("gn_no_tile", 0) || !gn_tile_shape_ok(B, HW, C))
         return false;
     if (!(aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)))
         return false;
     GnGeom g;
-    const size_t budget = (size_t)tune_get("gn_fwd_budget_kb", 64) * 1024;
-    if (!gn_pick_geometry(&g, HW, C, G, 1, tune_get("gn_fwd_ct", 0), tune_get("gn_fwd_cs", 0), budget))
+    const size_t budget = (size_t)tune_get("gn_fwd_budget_kb", 96) * 1024;
+    if (!gn_pick_geometry(&g, B, HW, C, G, 1, tune_get("gn_fwd_ct", 0), tune_get("gn_fwd_cs", 0), budget,
+            tune_get("gn_ctas_per_sm", 2)))
         return false;
-    const size_t smem = gn_smem_bytes(g, 1);
+    const size_t smem = gn_smem_bytes(g);
     if (smem > (size_t)GN_MAX_DYN_SMEM || !gn_allow_big_smem(gn_fwd_tile<ACT>, smem_ok))
         return false;
     CUtensorMap map_x, map_y;
@@ -685,13 +823,178 @@ static bool gn_forward_tile(float* y, float* mu, float* rstd, const float* x, co
     return true;
 }
 
+
+// ---------------------------------------------------------------------------
+// strip (register-resident) dispatch
+// ---------------------------------------------------------------------------
+struct StripPlan {
+    int NT, VPT;
+    StripGeom g;
+    size_t smem;
+};
+
+// Chooses CTA size and strip width Ct such that all HW rows of a strip fit the CTA's
+// registers: HW <= (NT / (Ct/4)) * VPT.  Wider strips mean longer contiguous runs in memory.
+// (Splitting the rows of a wider strip over a cluster was measured and is slower than
+// narrower strips without one: the cluster barrier lengthens every CTA's critical path.)
+static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt, int force_ct, int force_nt,
+    int ctas_per_sm_hint)
+{
+    if (C % 4 != 0 || C % G != 0)
+        return false;
+    const int cpg = C / G;
+    long best = -1;
+    const int nts[3] = { 512, 1024, 256 };
+    for (int ni = 0; ni < 3; ++ni) {
+        const int NT = nts[ni];
+        if (force_nt > 0 ? NT != force_nt : NT == 256)
+            continue;  // 256-thread CTAs only on request
+        for (int Ct = 4; Ct <= C && Ct <= 1024; Ct += 4) {
+            if (C % Ct != 0 || Ct % cpg != 0)
+                continue;
+            if (force_ct > 0 && Ct != force_ct)
+                continue;
+            const int Q = Ct / 4;
+            if (Q > NT || NT % Q != 0)
+                continue;
+            const int rstep = NT / Q;
+            const int need = (HW + rstep - 1) / rstep;
+            int vpt = 2;
+            while (vpt < need)
+                vpt *= 2;
+            if (vpt > max_vpt)
+                continue;
+            long score = 0;
+            if (Ct * 4 >= 64)
+                score += 1000000;
+            score += (long)Ct * 100;
+            score += (long)(100.0 * HW / ((double)rstep * vpt));  // register utilisation
+            if (NT == 512)
+                score += 5000;  // two CTAs per SM overlap each other's phases
+            if (score > best) {
+                best = score;
+                out->NT = NT;
+                out->VPT = vpt;
+                StripGeom g;
+                g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = rstep;
+                g.Gt = Ct / cpg; g.nct = C / Ct;
+                g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+                out->g = g;
+                const int red = (Q <= 32 && 32 % Q == 0) ? 2 * (NT / 32) * Ct : 2 * NT * 4;
+                out->smem = (size_t)(red + 2 * Ct + 2 * g.Gt) * sizeof(float);
+            }
+        }
+    }
+    if (best < 0)
+        return false;
+    // Start the second CTA of every SM half a strip period later (only the first wave needs it:
+    // later CTAs inherit the phase of the slot they replace).
+    const long grid = (long)B * out->g.nct;
+    const int per_sm = ctas_per_sm_hint > 0 ? ctas_per_sm_hint : (out->NT <= 256 ? 4 : (out->NT <= 512 ? 2 : 1));
+    const int ns = tune_get("gn_stagger_ns", -1);
+    if (per_sm >= 2 && grid > (long)sm_count() * per_sm && ns != 0) {
+        out->g.stagger_lo = sm_count();
+        out->g.stagger_hi = sm_count() * 2;
+        out->g.stagger_ns = ns > 0 ? ns : 3000;
+    }
+    return true;
+}
+
+template <class... KArgs, class... Args>
+static bool strip_launch(void (*kernel)(KArgs...), long grid, int NT, size_t smem, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)NT, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        report_error(__FILE__, __LINE__, "groupnorm strip launch failed: %s", cudaGetErrorString(e));
+        return false;
+    }
+    count_launch();
+    return true;
+}
+
+#define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
+    if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
+        return strip_launch(gn_fwd_strip<NTv, VPTv, ACT>, grid, NTv, plan.smem, s, y, mu, rstd, x, gamma, \
+            beta, plan.g, eps);
+#define STRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
+    if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
+        return strip_launch(gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, plan.smem, s, dx, sc.partials,  \
+            sc.tickets, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, plan.g, B);
+
+template <int ACT>
+static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, const float* gamma,
+    const float* beta, int B, int HW, int C, int G, float eps, cudaStream_t s)
+{
+    if constexpr (ACT != ACT_IDENTITY && ACT != ACT_SILU && ACT != ACT_MP_SILU) {
+        return false;
+    } else {
+        if (tune_get("gn_force_generic", 0) || tune_get("gn_no_strip", 0))
+            return false;
+        if (!(aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)) || (long)B * HW * C >= 2147483648L)
+            return false;
+        StripPlan plan;
+        if (!strip_plan(&plan, B, HW, C, G, 8, tune_get("gn_fwd_strip_ct", 0), tune_get("gn_fwd_strip_nt", 0), 0))
+            return false;
+        const long grid = (long)B * plan.g.nct;
+        if (grid > 2147483647L)
+            return false;
+        STRIP_FWD_CASE(1024, 2) STRIP_FWD_CASE(1024, 4) STRIP_FWD_CASE(1024, 8)
+        STRIP_FWD_CASE(512, 2) STRIP_FWD_CASE(512, 4) STRIP_FWD_CASE(512, 8)
+        STRIP_FWD_CASE(256, 2) STRIP_FWD_CASE(256, 4) STRIP_FWD_CASE(256, 8)
+        return false;
+    }
+}
+
+template <int ACT>
+static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+    const float* gamma, const float* beta, const float* mu, const float* rstd, int B, int HW, int C, int G,
+    cudaStream_t s)
+{
+    if constexpr (ACT != ACT_IDENTITY && ACT != ACT_SILU && ACT != ACT_MP_SILU) {
+        return false;
+    } else {
+        if (tune_get("gn_force_generic", 0) || tune_get("gn_no_strip", 0))
+            return false;
+        if (!(aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(gamma)) || (long)B * HW * C >= 2147483648L)
+            return false;
+        if (ACT != ACT_IDENTITY && !aligned16(beta))
+            return false;
+        StripPlan plan;
+        const int force_nt = tune_get("gn_bwd_strip_nt", 0);
+        // 512-thread CTAs may hold 8 rows per tensor (one CTA per SM, 128 registers per thread)
+        const int max_vpt = tune_get("gn_bwd_strip_vpt", 4);
+        if (!strip_plan(&plan, B, HW, C, G, max_vpt, tune_get("gn_bwd_strip_ct", 0), force_nt, max_vpt == 8 ? 1 : 0))
+            return false;
+        if (plan.VPT == 8 && plan.NT != 512)
+            return false;
+        const long grid = (long)B * plan.g.nct;
+        if (grid > 2147483647L)
+            return false;
+        Scratch sc;
+        if (!scratch_get(s, (size_t)2 * B * C, (size_t)plan.g.nct, &sc))
+            return false;
+        STRIP_BWD_CASE(1024, 2, 1) STRIP_BWD_CASE(1024, 4, 1)
+        STRIP_BWD_CASE(512, 2, 2) STRIP_BWD_CASE(512, 4, 2) STRIP_BWD_CASE(512, 8, 1)
+        STRIP_BWD_CASE(256, 2, 4) STRIP_BWD_CASE(256, 4, 4)
+        return false;
+    }
+}
+
 template <int ACT>
 static void gn_forward(float* y, float* mu, float* rstd, const float* x, const float* gamma, const float* beta,
     int B, int HW, int C, int G, float eps, cudaStream_t s)
 {
+    if (gn_forward_strip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
+        return;
     if (gn_forward_tile<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
-    gn_fwd_generic<ACT><<<B * G, GN_THREADS, 0, s>>>(y, mu, rstd, x, gamma, beta, HW, C, G, eps);
+    gn_fwd_generic<ACT><<<B * G, GN_GENERIC_THREADS, 0, s>>>(y, mu, rstd, x, gamma, beta, HW, C, G, eps);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -702,17 +1005,18 @@ static bool gn_backward_tile(float* dx, float* dgamma, float* dbeta, const float
     cudaStream_t s)
 {
     static bool smem_ok[64] = { false };
-    if (tune_get("gn_force_generic", 0) || !gn_tile_shape_ok(B, HW, C))
+    if (tune_get("gn_force_generic", 0) || tune_get("gn_no_tile", 0) || !gn_tile_shape_ok(B, HW, C))
         return false;
     if (!(aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(gamma)))
         return false;
     if (ACT != ACT_IDENTITY && !aligned16(beta))
         return false;
     GnGeom g;
-    const size_t budget = (size_t)tune_get("gn_bwd_budget_kb", 64) * 1024;
-    if (!gn_pick_geometry(&g, HW, C, G, 2, tune_get("gn_bwd_ct", 0), tune_get("gn_bwd_cs", 0), budget))
+    const size_t budget = (size_t)tune_get("gn_bwd_budget_kb", 96) * 1024;
+    if (!gn_pick_geometry(&g, B, HW, C, G, 2, tune_get("gn_bwd_ct", 0), tune_get("gn_bwd_cs", 0), budget,
+            tune_get("gn_ctas_per_sm", 2)))
         return false;
-    const size_t smem = gn_smem_bytes(g, 2);
+    const size_t smem = gn_smem_bytes(g);
     if (smem > (size_t)GN_MAX_DYN_SMEM || !gn_allow_big_smem(gn_bwd_tile<ACT>, smem_ok))
         return false;
     CUtensorMap map_x, map_dy, map_dx;
@@ -746,12 +1050,14 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     const float* gamma, const float* beta, const float* mu, const float* rstd, int B, int HW, int C, int G,
     cudaStream_t s)
 {
+    if (gn_backward_strip<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
+        return;
     if (gn_backward_tile<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
         return;
     Scratch sc;
     B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed");
     B200_REQUIRE(B <= 65535, "groupnorm_backward: batch %d too large for the generic path", B);
-    gn_bwd_dx_generic<ACT><<<B * G, GN_THREADS, 0, s>>>(dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
+    gn_bwd_dx_generic<ACT><<<B * G, GN_GENERIC_THREADS, 0, s>>>(dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
     count_launch();
     B200_CHECK_LAUNCH();
     gn_bwd_param_generic<ACT><<<dim3((C + 31) / 32, B), dim3(32, 8), 0, s>>>(sc.partials, dy, x, gamma, beta, mu,

@@ -1,0 +1,319 @@
+// Register-resident GroupNorm "strip" kernels (included by groupnorm.cu).
+//
+// One CTA owns the strip [all HW rows of one sample] x [Ct channels covering
+// whole groups] and keeps it entirely in REGISTERS: thread t holds the float4
+// column q = t % Q (Q = Ct/4) of rows rl, rl+RSTEP, ... (RSTEP = NT/Q), VPT rows
+// in all.  Every load of the strip is issued before the first is consumed, so a
+// single CTA has its whole strip (up to 128 KB) in flight; statistics, the
+// normalised output (or dx) and the parameter-gradient partials are all computed
+// from registers, so x (and dy) cross HBM exactly once and nothing but a few
+// hundred floats of partial sums ever touches shared memory.  The CTA needs two
+// __syncthreads per strip and no cluster, no TMA descriptor and no staging
+// buffer; it is the GroupNorm analogue of the warp-per-row LayerNorm kernel.
+//
+// The strip must fit the register file: HW <= RSTEP * VPT with VPT <= 8
+// (forward) or <= 4 per tensor (backward).  Larger samples take the TMA /
+// cluster tile kernels.
+#pragma once
+
+namespace b200 {
+
+template <int NT>
+struct StripSmem {
+    static constexpr int NW = NT / 32;
+};
+
+// Folds per-thread float4 pairs over all row lanes of the CTA; afterwards
+// chan[c] / chan[Ct + c] hold the totals of channel c.  `red` has 2*NW*Ct floats
+// when Q divides 32 (shuffle path), else 2*NT*4 floats.
+template <int NT>
+__device__ __forceinline__ void strip_fold(float* red, float* chan, int Q, int Ct, int q, int rl, float4 a, float4 b)
+{
+    constexpr int NW = NT / 32;
+    const int t = threadIdx.x;
+    if (Q <= 32 && 32 % Q == 0) {
+        for (int off = Q; off < 32; off <<= 1) {
+            a = shfl_xor4(a, off);
+            b = shfl_xor4(b, off);
+        }
+        const int lane = t & 31, warp = t >> 5;
+        if (lane < Q) {
+            reinterpret_cast<float4*>(red)[warp * Q + lane] = a;
+            reinterpret_cast<float4*>(red + NW * Ct)[warp * Q + lane] = b;
+        }
+        __syncthreads();
+        if (t < Ct) {
+            float sa = 0.0f, sb = 0.0f;
+#pragma unroll 8
+            for (int w = 0; w < NW; ++w) {
+                sa += red[w * Ct + t];
+                sb += red[NW * Ct + w * Ct + t];
+            }
+            chan[t] = sa;
+            chan[Ct + t] = sb;
+        }
+    } else {
+        const int rstep = NT / Q;
+        reinterpret_cast<float4*>(red)[rl * Q + q] = a;
+        reinterpret_cast<float4*>(red + NT * 4)[rl * Q + q] = b;
+        __syncthreads();
+        if (t < Ct) {
+            float sa = 0.0f, sb = 0.0f;
+            for (int r = 0; r < rstep; ++r) {
+                sa += red[r * Ct + t];
+                sb += red[NT * 4 + r * Ct + t];
+            }
+            chan[t] = sa;
+            chan[Ct + t] = sb;
+        }
+    }
+    __syncthreads();
+}
+
+struct StripGeom {
+    int HW, C, G, cpg, Ct, Q, RSTEP, Gt, nct;
+    // CTAs with stagger_lo <= blockIdx.x < stagger_hi start stagger_ns later, so that the CTAs
+    // sharing an SM run out of phase (one loads while the other computes and stores)
+    int stagger_lo, stagger_hi, stagger_ns;
+};
+
+// ---------------------------------------------------------------------------
+// forward: grid = B * nct, block = NT
+// ---------------------------------------------------------------------------
+template <int NT, int VPT, int ACT>
+__global__ void __launch_bounds__(NT, (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))) gn_fwd_strip(float* __restrict__ y, float* __restrict__ mu,
+    float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const StripGeom g, const float eps)
+{
+    extern __shared__ float strip_smem[];
+    float* red = strip_smem;
+    const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * (NT / 32) * g.Ct : 2 * NT * 4;
+    float* chan = red + red_floats;      // 2*Ct
+    float* gstat = chan + 2 * g.Ct;      // 2*Gt
+    const int t = threadIdx.x;
+    const int ctile = blockIdx.x % g.nct, b = blockIdx.x / g.nct;
+    const int c0 = ctile * g.Ct;
+    const int q = t % g.Q, rl = t / g.Q;
+    const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
+    if ((int)blockIdx.x >= g.stagger_lo && (int)blockIdx.x < g.stagger_hi)
+        __nanosleep(g.stagger_ns);
+
+    // per-channel shift K = row 0 of the sample (same for every thread of a column)
+    const float4 K = __ldg(reinterpret_cast<const float4*>(x + base));
+    float4 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        v[j] = K;  // rows past the end contribute zero to the shifted sums
+        if (r < g.HW)
+            v[j] = __ldcs(reinterpret_cast<const float4*>(x + base + (size_t)r * g.C));
+    }
+    float4 s1 = make_float4(0.f, 0.f, 0.f, 0.f), s2 = s1;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const float d0 = v[j].x - K.x, d1 = v[j].y - K.y, d2 = v[j].z - K.z, d3 = v[j].w - K.w;
+        s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
+        s2.x = fmaf(d0, d0, s2.x); s2.y = fmaf(d1, d1, s2.y); s2.z = fmaf(d2, d2, s2.z); s2.w = fmaf(d3, d3, s2.w);
+    }
+    strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, s1, s2);
+
+    // group statistics: thread grp < Gt combines its cpg channels
+    if (t < g.Gt) {
+        const float n = (float)g.HW * (float)g.cpg;
+        const float* xrow0 = x + (size_t)b * g.HW * g.C + c0 + t * g.cpg;
+        // mean = (sum_c HW*K_c + S1_c) / n ;  centred second moment via the shift identity
+        float msum = 0.0f;
+        for (int cl = 0; cl < g.cpg; ++cl)
+            msum += chan[t * g.cpg + cl] + (float)g.HW * __ldg(xrow0 + cl);
+        const float mean = msum / n;
+        float m2 = 0.0f;
+        for (int cl = 0; cl < g.cpg; ++cl) {
+            const int ch = t * g.cpg + cl;
+            const float dk = __ldg(xrow0 + cl) - mean;
+            m2 += chan[g.Ct + ch] + 2.0f * dk * chan[ch] + (float)g.HW * dk * dk;
+        }
+        const float rs = rsqrtf(m2 / n + eps);
+        gstat[t] = mean;
+        gstat[g.Gt + t] = rs;
+        mu[b * g.G + c0 / g.cpg + t] = mean;
+        rstd[b * g.G + c0 / g.cpg + t] = rs;
+    }
+    __syncthreads();
+
+    const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+    const float4 be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+    const int cb = 4 * q;
+    const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
+    float4 sc, sh;
+    sc.x = ga.x * gstat[g.Gt + g0]; sh.x = be.x - gstat[g0] * sc.x;
+    sc.y = ga.y * gstat[g.Gt + g1]; sh.y = be.y - gstat[g1] * sc.y;
+    sc.z = ga.z * gstat[g.Gt + g2]; sh.z = be.z - gstat[g2] * sc.z;
+    sc.w = ga.w * gstat[g.Gt + g3]; sh.w = be.w - gstat[g3] * sc.w;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        if (r < g.HW) {
+            float4 o;
+            o.x = act_value<ACT>(fmaf(v[j].x, sc.x, sh.x));
+            o.y = act_value<ACT>(fmaf(v[j].y, sc.y, sh.y));
+            o.z = act_value<ACT>(fmaf(v[j].z, sc.z, sh.z));
+            o.w = act_value<ACT>(fmaf(v[j].w, sc.w, sh.w));
+            __stcs(reinterpret_cast<float4*>(y + base + (size_t)r * g.C), o);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// backward: grid = B * nct, block = NT
+// partials layout: [nct][B][2*Ct] (first Ct: dgamma, next Ct: dbeta); the last CTA of
+// a channel tile (atomic ticket) adds the B rows in a fixed order.
+// ---------------------------------------------------------------------------
+template <int NT, int VPT, int ACT, int MB>
+__global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
+    float* __restrict__ partials, unsigned int* __restrict__ tickets, float* __restrict__ dgamma,
+    float* __restrict__ dbeta, const float* __restrict__ dy, const float* __restrict__ x,
+    const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mu,
+    const float* __restrict__ rstd, const StripGeom g, const int B)
+{
+    extern __shared__ float strip_smem[];
+    __shared__ int s_is_last;
+    constexpr int NW = NT / 32;
+    float* red = strip_smem;
+    const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * NW * g.Ct : 2 * NT * 4;
+    float* chan = red + red_floats;
+    float* gstat = chan + 2 * g.Ct;
+    const int t = threadIdx.x;
+    const int ctile = blockIdx.x % g.nct, b = blockIdx.x / g.nct;
+    const int c0 = ctile * g.Ct;
+    const int q = t % g.Q, rl = t / g.Q;
+    const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
+    const int cb = 4 * q;
+    if ((int)blockIdx.x >= g.stagger_lo && (int)blockIdx.x < g.stagger_hi)
+        __nanosleep(g.stagger_ns);
+    const int gl0 = (cb + 0) / g.cpg, gl1 = (cb + 1) / g.cpg, gl2 = (cb + 2) / g.cpg, gl3 = (cb + 3) / g.cpg;
+
+    float4 xv[VPT], dv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        dv[j] = xv[j];
+        if (r < g.HW) {
+            xv[j] = __ldcs(reinterpret_cast<const float4*>(x + base + (size_t)r * g.C));
+            dv[j] = __ldcs(reinterpret_cast<const float4*>(dy + base + (size_t)r * g.C));
+        }
+    }
+    const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+    float4 be = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ACT != ACT_IDENTITY)
+        be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+    const int gbase = b * g.G + c0 / g.cpg;
+    float4 rs4, nm4;
+    rs4.x = __ldg(rstd + gbase + gl0); nm4.x = -__ldg(mu + gbase + gl0) * rs4.x;
+    rs4.y = __ldg(rstd + gbase + gl1); nm4.y = -__ldg(mu + gbase + gl1) * rs4.y;
+    rs4.z = __ldg(rstd + gbase + gl2); nm4.z = -__ldg(mu + gbase + gl2) * rs4.z;
+    rs4.w = __ldg(rstd + gbase + gl3); nm4.w = -__ldg(mu + gbase + gl3) * rs4.w;
+
+    float4 sA = make_float4(0.f, 0.f, 0.f, 0.f), sB = sA;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        if (r < g.HW) {
+            xv[j].x = fmaf(xv[j].x, rs4.x, nm4.x);
+            xv[j].y = fmaf(xv[j].y, rs4.y, nm4.y);
+            xv[j].z = fmaf(xv[j].z, rs4.z, nm4.z);
+            xv[j].w = fmaf(xv[j].w, rs4.w, nm4.w);
+            if (ACT != ACT_IDENTITY) {
+                dv[j].x *= act_slope<ACT>(fmaf(ga.x, xv[j].x, be.x));
+                dv[j].y *= act_slope<ACT>(fmaf(ga.y, xv[j].y, be.y));
+                dv[j].z *= act_slope<ACT>(fmaf(ga.z, xv[j].z, be.z));
+                dv[j].w *= act_slope<ACT>(fmaf(ga.w, xv[j].w, be.w));
+            }
+            sA.x += dv[j].x; sA.y += dv[j].y; sA.z += dv[j].z; sA.w += dv[j].w;
+            sB.x = fmaf(dv[j].x, xv[j].x, sB.x); sB.y = fmaf(dv[j].y, xv[j].y, sB.y);
+            sB.z = fmaf(dv[j].z, xv[j].z, sB.z); sB.w = fmaf(dv[j].w, xv[j].w, sB.w);
+        }
+    }
+    // chan[c] = sum_rows dy (-> dbeta), chan[Ct+c] = sum_rows dy*xhat (-> dgamma)
+    strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, sA, sB);
+
+    if (t < g.Gt) {
+        float sg = 0.0f, sgx = 0.0f;
+        for (int cl = 0; cl < g.cpg; ++cl) {
+            const int ch = t * g.cpg + cl;
+            const float gm = __ldg(gamma + c0 + ch);
+            sg = fmaf(gm, chan[ch], sg);
+            sgx = fmaf(gm, chan[g.Ct + ch], sgx);
+        }
+        const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
+        gstat[t] = sg * inv_n;
+        gstat[g.Gt + t] = sgx * inv_n;
+    }
+    if (t < g.Ct) {
+        float* dst = partials + ((size_t)ctile * B + b) * (2 * g.Ct);
+        dst[t] = chan[g.Ct + t];
+        dst[g.Ct + t] = chan[t];
+    }
+    __syncthreads();
+
+    float4 mg, mgx;
+    mg.x = gstat[gl0]; mgx.x = gstat[g.Gt + gl0];
+    mg.y = gstat[gl1]; mgx.y = gstat[g.Gt + gl1];
+    mg.z = gstat[gl2]; mgx.z = gstat[g.Gt + gl2];
+    mg.w = gstat[gl3]; mgx.w = gstat[g.Gt + gl3];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        if (r < g.HW) {
+            float4 o;
+            o.x = rs4.x * (fmaf(dv[j].x, ga.x, -mg.x) - xv[j].x * mgx.x);
+            o.y = rs4.y * (fmaf(dv[j].y, ga.y, -mg.y) - xv[j].y * mgx.y);
+            o.z = rs4.z * (fmaf(dv[j].z, ga.z, -mg.z) - xv[j].z * mgx.z);
+            o.w = rs4.w * (fmaf(dv[j].w, ga.w, -mg.w) - xv[j].w * mgx.w);
+            __stcs(reinterpret_cast<float4*>(dx + base + (size_t)r * g.C), o);
+        }
+    }
+
+    // ---- ticket: the last sample of this channel tile folds the B partial rows
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const unsigned old = atomicAdd(&tickets[ctile], 1u);
+        s_is_last = (old == (unsigned)B - 1u);
+    }
+    __syncthreads();
+    if (s_is_last) {
+        __threadfence();
+        const int nrows = B;
+        const int width = 2 * g.Ct;
+        const int nq = width / 4;
+        int lanes = NT / nq;
+        const int cap = red_floats / width;
+        if (lanes > cap)
+            lanes = cap;
+        const int qi = t % nq, bl = t / nq;
+        const float* src = partials + (size_t)ctile * nrows * width;
+        if (bl < lanes) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int bb = bl; bb < nrows; bb += lanes) {
+                const float4 p = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+            }
+            reinterpret_cast<float4*>(red)[bl * nq + qi] = acc;
+        }
+        __syncthreads();
+        for (int j = t; j < width; j += NT) {
+            float s = 0.0f;
+            for (int r = 0; r < lanes; ++r)
+                s += red[r * width + j];
+            if (j < g.Ct)
+                dgamma[c0 + j] = s;
+            else
+                dbeta[c0 + j - g.Ct] = s;
+        }
+        if (t == 0)
+            tickets[ctile] = 0;
+    }
+}
+
+}  // namespace b200

@@ -195,10 +195,12 @@ def test_tile_and_generic_groupnorm_agree(lib, orc):
 
 @pytest.mark.parametrize("ct,cs", [(8, 1), (16, 2), (32, 4), (64, 4), (64, 1), (32, 2)])
 def test_groupnorm_tile_geometries(lib, orc, ct, cs):
-    """Every (channel tile, cluster size) the heuristic may choose gives the same answer."""
-    p = dict(B=3, HW=196, C=64, G=32, act="mp_silu")
+    """The TMA / cluster tile kernels (the path for samples too large for the register
+    strips): every (channel tile, cluster size) the heuristic may choose gives the same answer."""
+    p = dict(B=5, HW=196, C=64, G=32, act="mp_silu")
     inp = cases.make_inputs("groupnorm", p, seed=31)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    lib.b200_tune_set(b"gn_no_strip", 1)
     for key in (b"gn_fwd_ct", b"gn_bwd_ct"):
         lib.b200_tune_set(key, ct)
     for key in (b"gn_fwd_cs", b"gn_bwd_cs"):
@@ -206,9 +208,66 @@ def test_groupnorm_tile_geometries(lib, orc, ct, cs):
     try:
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
-        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs"):
+        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs", b"gn_no_strip"):
             lib.b200_tune_set(key, 0)
     _check(got, ref, f"ct{ct}cs{cs}")
+
+
+def test_groupnorm_tile_kernels_persistent_loop(lib, orc):
+    """More work items than resident clusters, so every cluster loops and double-buffers."""
+    p = dict(B=40, HW=64, C=128, G=16, act="silu")
+    inp = cases.make_inputs("groupnorm", p, seed=33)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    lib.b200_tune_set(b"gn_no_strip", 1)
+    for key, val in ((b"gn_fwd_ct", 8), (b"gn_bwd_ct", 8), (b"gn_fwd_cs", 2), (b"gn_bwd_cs", 2)):
+        lib.b200_tune_set(key, val)
+    try:
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs", b"gn_no_strip"):
+            lib.b200_tune_set(key, 0)
+    _check(got, ref, "persistent")
+
+
+STRIP_KEYS = (b"gn_fwd_strip_nt", b"gn_bwd_strip_nt", b"gn_fwd_strip_ct", b"gn_bwd_strip_ct", b"gn_bwd_strip_vpt")
+
+
+@pytest.mark.parametrize("nt,fct,bct,bvpt", [(1024, 32, 16, 4), (512, 16, 8, 4), (1024, 8, 8, 4), (256, 8, 4, 4),
+                                             (512, 16, 16, 8), (512, 8, 8, 8)])
+def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
+    """The register-resident strip kernels with forced CTA size and strip width (ragged HW:
+    196 rows do not divide evenly over the row lanes)."""
+    p = dict(B=5, HW=196, C=64, G=32, act="silu")
+    inp = cases.make_inputs("groupnorm", p, seed=35)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    for key, val in zip(STRIP_KEYS, (nt, nt, fct, bct, bvpt)):
+        lib.b200_tune_set(key, val)
+    lib.b200_tune_set(b"gn_no_tile", 1)
+    try:
+        n0 = lib.b200_launch_count()
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+        assert lib.b200_launch_count() - n0 == 2, "expected one forward and one backward strip kernel"
+    finally:
+        for key in STRIP_KEYS + (b"gn_no_tile",):
+            lib.b200_tune_set(key, 0)
+        lib.b200_tune_set(b"gn_bwd_strip_vpt", 4)
+    _check(got, ref, f"strip nt{nt}")
+
+
+def test_groupnorm_strip_stagger_many_ctas(lib, orc):
+    """More strips than one wave of CTAs, so the staggered start of the second CTA per SM is exercised."""
+    p = dict(B=160, HW=64, C=32, G=8, act="silu")
+    inp = cases.make_inputs("groupnorm", p, seed=37)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    for key, val in ((b"gn_fwd_strip_ct", 8), (b"gn_bwd_strip_ct", 8), (b"gn_fwd_strip_nt", 512), (b"gn_bwd_strip_nt", 512)):
+        lib.b200_tune_set(key, val)
+    try:
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        for key in STRIP_KEYS:
+            lib.b200_tune_set(key, 0)
+        lib.b200_tune_set(b"gn_bwd_strip_vpt", 4)
+    _check(got, ref, "stagger")
 
 
 def test_multi_tensor_entry_points(pkg, lib, orc):
