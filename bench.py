@@ -375,9 +375,10 @@ def ops_table(lib, fused, peak):
 
 
 # ------------------------------------------------------------------------------------ CPU baseline
-def cpu_baseline(threads=None, samples=8):
+def cpu_baseline(threads=None, samples=16, min_seconds=8.0):
     """The plain-C port (oracle/layer_oracle.c, fp32 accumulation) on the host cores over a bounded
-    sample of the step: `samples` of the 256 images per GPU, same kernel sequence."""
+    sample of the step: `samples` of the 256 images per GPU, same kernel sequence, repeated until
+    about `min_seconds` of CPU time have been spent."""
     sys.path.insert(0, str(ROOT / "oracle"))
     orc = importlib.import_module("oracle")
     orc.load()
@@ -389,19 +390,29 @@ def cpu_baseline(threads=None, samples=8):
     dy = rng.standard_normal((samples, HW, C), dtype=np.float32)
     gam = (1 + 0.1 * rng.standard_normal(C)).astype(np.float32); bet = (0.1 * rng.standard_normal(C)).astype(np.float32)
     tt = rng.integers(0, 1000, samples).astype(np.float32)
-    t0 = time.perf_counter()
-    y, mu, rstd = orc.groupnorm_forward(x, gam, bet, G, 1e-5, "silu")
-    orc.groupnorm_backward(dy, x, gam, bet, mu, rstd, G, "silu")
-    y2, lmu, lrs = orc.layernorm_forward(x.reshape(-1, C), gam, bet, 1e-5)
-    orc.layernorm_backward(dy.reshape(-1, C), x.reshape(-1, C), gam, lmu, lrs)
-    orc.sinusoidal(tt, EMB, np.float32(math.log(1e4)))
-    dt = time.perf_counter() - t0
-    nbytes = STEP_BYTES * samples / B
+
+    def one():
+        y, mu, rstd = orc.groupnorm_forward(x, gam, bet, G, 1e-5, "silu")
+        orc.groupnorm_backward(dy, x, gam, bet, mu, rstd, G, "silu")
+        y2, lmu, lrs = orc.layernorm_forward(x.reshape(-1, C), gam, bet, 1e-5)
+        orc.layernorm_backward(dy.reshape(-1, C), x.reshape(-1, C), gam, lmu, lrs)
+        orc.sinusoidal(tt, EMB, np.float32(math.log(1e4)))
+
+    one()  # warm-up (page faults, thread pool)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        one()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or reps >= 200:
+            break
+    nbytes = STEP_BYTES * samples / B * reps
     orc.set_accumulate_double(True)
     orc.set_threads(1)
     return {"value": round(nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{samples} of the {B} samples of one step (same kernel sequence), {dt:.2f} s of CPU work, "
-                      f"OpenMP over {threads} threads; the reference has no CPU path, so this is the plain-C port"}
+            "sample": f"{samples} of the {B} samples of one step (same kernel sequence) x {reps} repeats, {dt:.1f} s of "
+                      f"CPU work, OpenMP over {threads} threads; the reference has no CPU path, so this is the "
+                      f"plain-C port of its kernels"}
 
 
 # ------------------------------------------------------------------------------------ main
@@ -502,7 +513,7 @@ def main():
         line["impl"] = "reference"
         line["reference_kind"] = ref_note
     if rank == 0:
-        if not args.no_cpu and world == 1 or args.impl == "reference":
+        if not args.no_cpu and (world == 1 or args.impl == "reference"):
             line["cpu_baseline"] = cpu_baseline()
         if not args.no_ops and world == 1:
             del step

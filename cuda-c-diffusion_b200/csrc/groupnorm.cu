@@ -968,7 +968,7 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
         StripPlan plan;
         const int force_nt = tune_get("gn_bwd_strip_nt", 0);
         // 512-thread CTAs may hold 8 rows per tensor (one CTA per SM, 128 registers per thread)
-        const int max_vpt = tune_get("gn_bwd_strip_vpt", 4);
+        const int max_vpt = tune_get("gn_bwd_strip_vpt", 8);
         if (!strip_plan(&plan, B, HW, C, G, max_vpt, tune_get("gn_bwd_strip_ct", 0), force_nt, max_vpt == 8 ? 1 : 0))
             return false;
         if (plan.VPT == 8 && plan.NT != 512)
