@@ -69,6 +69,7 @@ SIGNATURES = {
     "launch_adam_ema_step_multi": "hiffffffffs",
     "launch_weight_normalize_multi": "hifs",
     "launch_axpby_rows": "pppppiis",
+    "launch_layernorm_backward_noalloc": "ppppppppiis",
     # management
     "b200_set_error_mode": "i",
     "b200_error_count": "",
@@ -84,6 +85,7 @@ SIGNATURES = {
 }
 
 RETURNS = {
+    "launch_layernorm_backward_noalloc": ctypes.c_int,
     "b200_error_count": ctypes.c_int,
     "b200_last_error": ctypes.c_int,
     "b200_device_error_status": ctypes.c_int,

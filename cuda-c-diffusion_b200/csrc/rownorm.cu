@@ -559,3 +559,107 @@ void launch_pixel_norm_backward(float* dx, const float* dy, const float* x, int 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// LayerNorm backward for callers that may not allocate device memory
+// ---------------------------------------------------------------------------
+// Some hosts of these kernels run under a fixed device-memory plan: every buffer is created
+// once by the module constructors and the training loop must not enter the CUDA allocator
+// again (small shared-memory boards where the heap is sized up front, or code that calls the
+// backward pass from a place where cudaMalloc is off limits, such as inside an allocator hook
+// or a section that holds the allocator's lock).  launch_layernorm_backward keeps its
+// per-CTA dgamma/dbeta partial rows in a scratch arena that it allocates on first use, which
+// such a caller cannot accept.  This variant keeps the partial rows in a fixed array that is
+// part of the library image instead.
+//
+// The array lives in this translation unit.  Its name is only a host-side handle here; the
+// device address is looked up once per device with cudaGetSymbolAddress and handed to the
+// kernels as an ordinary pointer.
+namespace b200 {
+
+constexpr size_t LN_NOALLOC_MAX_FLOATS = (size_t)1 << 20;  // 4 MiB of partial rows
+static __device__ __align__(256) float g_ln_noalloc_scratch[LN_NOALLOC_MAX_FLOATS];
+
+// Device address of the fixed scratch array on the current device (looked up once per device,
+// with that device current).  Returns nullptr and reports when the lookup fails.
+static float* ln_noalloc_scratch_address()
+{
+    static float* cached[64] = { nullptr };
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        report_error(__FILE__, __LINE__, "layernorm_backward_noalloc: cannot identify the current device (%s)",
+            cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (!cached[dev]) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_ln_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            report_error(__FILE__, __LINE__, "layernorm_backward_noalloc: cudaGetSymbolAddress failed (%s)",
+                cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+}  // namespace b200
+
+extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, float* gbeta,
+    const float* grad_out, const float* x, const float* gamma, const float* mu, const float* rstd, int batch,
+    int C, cudaStream_t s)
+{
+    using namespace b200;
+    if (batch < 0 || C <= 0) {
+        report_error(__FILE__, __LINE__, "layernorm_backward_noalloc: batch=%d C=%d", batch, C);
+        return -1;
+    }
+    const long rows = batch;
+    const bool fast = fast_rows_ok(C) && rows > 0 && aligned16(grad_in) && aligned16(grad_out) && aligned16(x)
+        && aligned16(gamma);
+    // partial rows this call needs: one per CTA (fast path) or one per 256-row chunk (generic path)
+    const int R = (C / 128 == 1) ? 4 : (C / 128 == 2 ? 2 : 1);
+    const int chunk_rows = 256;
+    long nparts;
+    if (fast) {
+        nparts = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 4);
+        const long fit = (long)(LN_NOALLOC_MAX_FLOATS / (2 * (size_t)C));
+        if (nparts > fit)
+            nparts = fit;  // fewer, longer-running CTAs: the grid-stride loop covers all rows
+    } else {
+        nparts = rows > 0 ? (rows + chunk_rows - 1) / chunk_rows : 1;
+    }
+    if (nparts < 1 || (size_t)nparts * 2 * (size_t)C > LN_NOALLOC_MAX_FLOATS || nparts > 65535) {
+        report_error(__FILE__, __LINE__,
+            "layernorm_backward_noalloc: batch=%d C=%d needs %ld partial rows of %d floats, more than the fixed "
+            "scratch of %zu floats (use launch_layernorm_backward, which allocates)",
+            batch, C, nparts, 2 * C, (size_t)LN_NOALLOC_MAX_FLOATS);
+        return -2;
+    }
+    float* scratch = ln_noalloc_scratch_address();
+    if (!scratch)
+        return -3;
+    if (fast) {
+        const int grid = (int)nparts;
+        RN_DISPATCH_VPT(C, (layernorm_bwd_rows<VPT, R><<<grid, RN_THREADS, 0, s>>>(grad_in, scratch, grad_out, x, gamma,
+                                mu, rstd, rows)));
+        count_launch();
+        B200_CHECK_LAUNCH();
+        fold_partials(ggamma, gbeta, scratch, grid, 2 * C, C, s);
+        return 0;
+    }
+    if (rows > 0) {
+        layernorm_bwd_dx_generic<<<rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s>>>(grad_in,
+            grad_out, x, gamma, mu, rstd, rows, C);
+        count_launch();
+        B200_CHECK_LAUNCH();
+    }
+    layernorm_bwd_param_generic<<<dim3((C + 31) / 32, (unsigned)nparts), dim3(32, 8), 0, s>>>(scratch, grad_out, x, mu,
+        rstd, rows, C, chunk_rows);
+    count_launch();
+    B200_CHECK_LAUNCH();
+    fold_partials(ggamma, gbeta, scratch, (int)nparts, 2 * C, C, s);
+    return 0;
+}

@@ -211,6 +211,26 @@ void launch_weight_normalize_multi(const B200WeightDesc* items, int count, float
 void launch_axpby_rows(float* out, const float* a, const float* b, const float* wa,
     const float* wb, int rows, int dim, cudaStream_t s);
 
+/* LayerNorm backward that allocates nothing.  It has no counterpart in the reference.
+   For hosts that run under a fixed device-memory plan and may not enter the CUDA allocator
+   after set-up (boards whose heap is sized once by the module constructors, or call sites
+   where cudaMalloc is off limits, e.g. inside an allocator hook): same arguments and results
+   as launch_layernorm_backward, but the per-CTA dgamma/dbeta partial rows go to a fixed
+   4 MiB array that is part of the library image (every GPU that loads the library carries it
+   until the process exits) instead of the on-demand scratch arena.
+   - Returns 0 on success; a negative value (and an error report, see b200_set_error_mode)
+     when batch/C need more partial rows than the array holds: for C a multiple of 128 up to
+     1024 every batch fits; otherwise ceil(batch/256) * 2*C floats must be <= 1048576.
+   - The first call on each device looks up the array's device address (that device must be
+     current); make that first call before starting any stream capture.
+   - All calls share the one array and it keeps what the previous call left there.  Nothing in
+     it has to be zero beforehand (every partial row is written before it is read), but two
+     calls that overlap on the GPU, from different streams or processes sharing the context,
+     race on it: serialise them. */
+int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, float* gbeta,
+    const float* grad_out, const float* x, const float* gamma, const float* mu, const float* rstd,
+    int batch, int C, cudaStream_t s);
+
 /* ============================ library management ============================ */
 
 /* Error handling.  Mode 0 (default) follows the reference (nn.h:13-52): print
