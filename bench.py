@@ -51,6 +51,16 @@ F = ctypes.c_float
 P = lambda t: ctypes.c_void_p(t.data_ptr())
 
 
+def set_batch(b):
+    """Shrinks the per-GPU batch (profiler captures on a small case); the default 256 is the benchmark."""
+    global B, NEL, STEP_BYTES, KERNEL_BYTES
+    B = b
+    NEL = B * HW * C
+    STEP_BYTES = 10 * NEL * 4 + B * EMB * 4
+    KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd": 2 * NEL * 4,
+                    "ln_bwd": 3 * NEL * 4, "sinusoidal": B * EMB * 4}
+
+
 def measured_peak():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -415,6 +425,38 @@ def cpu_baseline(threads=None, samples=16, min_seconds=8.0):
                       f"plain-C port of its kernels"}
 
 
+# ------------------------------------------------------------------------------------ EDM UNet training step
+def edm_train_images_per_s(binary, batch=256, steps=(4, 44)):
+    """Images/s of the reference's own EDM trainer (edm/main_edm.c + diffusion/train.c + every host module,
+    unmodified) with the given kernel backend linked in.  Config: channels 64/128/128, emb 128, 1 head, t 0.3,
+    batch 256, Adam lr 1e-3, EMA 0.999, TF32 GEMMs, synthetic 28x28 images (pixel -1 with p=0.8, else U(-1,1)).
+    The program has no timer, so two runs with different step counts are timed and the difference is used."""
+    import tempfile
+    if not Path(binary).exists():
+        return None
+    with tempfile.TemporaryDirectory() as tmp:
+        rng = np.random.default_rng(0)
+        n = 4096
+        img = np.where(rng.random((n, 28, 28)) < 0.8, -1.0, rng.uniform(-1, 1, (n, 28, 28))).astype(np.float32)
+        img.tofile(os.path.join(tmp, "images.bin"))
+        times = []
+        for st in steps:
+            ini = os.path.join(tmp, f"edm_{st}.ini")
+            with open(ini, "w") as f:
+                f.write(f"channels = 64,128,128\nemb_dim = 128\nheads = 1\nt = 0.3\nbatch_size = {batch}\n"
+                        f"train_steps = {st}\nlr = 1e-3\nlr_warmup = 500\nlr_ref = 5000\nema_decay = 0.999\n"
+                        f"tf32 = 1\nsample_steps = 1\nvis_batch = 1\nimages = {tmp}/images.bin\nH = 28\nW = 28\nC = 1\n")
+            t0 = time.perf_counter()
+            res = subprocess.run([str(binary), ini], cwd=tmp, capture_output=True, text=True, timeout=900)
+            times.append(time.perf_counter() - t0)
+            if res.returncode != 0:
+                return {"error": (res.stderr or res.stdout)[-300:]}
+        dt = times[1] - times[0]
+        nst = steps[1] - steps[0]
+        return {"images_per_s": round(batch * nst / dt, 1), "ms_per_step": round(dt / nst * 1e3, 2), "batch": batch,
+                "steps_timed": nst, "how": "wall-clock difference of two runs of the unmodified reference trainer"}
+
+
 # ------------------------------------------------------------------------------------ main
 KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd": 2 * NEL * 4, "ln_bwd": 3 * NEL * 4,
                 "sinusoidal": B * EMB * 4}
@@ -431,7 +473,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--batch", type=int, default=256, help="samples per GPU; values other than 256 are for profiling only")
     args = ap.parse_args()
+    if args.batch != 256:
+        set_batch(args.batch)
     args.warmup = max(args.warmup, 3)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -483,7 +529,10 @@ def main():
         launches = int(launches * args.steps / (args.steps + args.warmup))
     clocks = cs.summary()
     e2e_k = max(3, min(args.steps, 10))
-    e2e_ms, h2d, d2h = e2e_steps(step, e2e_k, 3, world)
+    if args.no_e2e:
+        e2e_ms, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_ms, h2d, d2h = e2e_steps(step, e2e_k, 3, world)
 
     value = world * STEP_BYTES * args.steps / (ms * 1e-3) / 1e9
     e2e_value = world * STEP_BYTES * e2e_k / (e2e_ms * 1e-3) / 1e9
@@ -494,7 +543,7 @@ def main():
         "metric": "fused norm/act fwd+bwd HBM GB/s", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[2]: DDPM block kernels, fp32 NHWC [256,32,32,256] per GPU: GroupNorm(32)+affine+SiLU "
+        "config": {"batch_per_gpu": B, "workload": "configs[2]: DDPM block kernels, fp32 NHWC [256,32,32,256] per GPU: GroupNorm(32)+affine+SiLU "
                                "fused fwd+bwd, LayerNorm C=256 fwd+bwd, sinusoidal dim 512; batch-sharded",
                    "l2": "inputs larger than L2 (each tensor 268 MB vs 126 MB L2); no flush needed",
                    "algorithmic_bytes_per_step": STEP_BYTES, "seed": 1234},
@@ -519,6 +568,10 @@ def main():
             del step
             torch.cuda.empty_cache()
             line["ops"] = ops_table(lib_run, fused, peak)
+            exe = ROOT / "oracle" / "_ref" / ("edm_demo_b200" if args.impl == "b200" else "edm_demo_ref")
+            edm = edm_train_images_per_s(exe)
+            if edm is not None:
+                line["edm_unet_train"] = edm
         print(json.dumps(line))
     if world > 1:
         torch.distributed.barrier()

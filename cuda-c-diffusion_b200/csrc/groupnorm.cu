@@ -891,11 +891,11 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
     // later CTAs inherit the phase of the slot they replace).
     const long grid = (long)B * out->g.nct;
     const int per_sm = ctas_per_sm_hint > 0 ? ctas_per_sm_hint : (out->NT <= 256 ? 4 : (out->NT <= 512 ? 2 : 1));
-    const int ns = tune_get("gn_stagger_ns", -1);
-    if (per_sm >= 2 && grid > (long)sm_count() * per_sm && ns != 0) {
+    const int ns = tune_get("gn_stagger_ns", 0);  // measured: no effect on B200, so off unless requested
+    if (per_sm >= 2 && grid > (long)sm_count() * per_sm && ns > 0) {
         out->g.stagger_lo = sm_count();
         out->g.stagger_hi = sm_count() * 2;
-        out->g.stagger_ns = ns > 0 ? ns : 3000;
+        out->g.stagger_ns = ns;
     }
     return true;
 }
@@ -917,6 +917,36 @@ static bool strip_launch(void (*kernel)(KArgs...), long grid, int NT, size_t sme
     count_launch();
     return true;
 }
+
+template <class... KArgs, class... Args>
+static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, int NT, size_t smem, cudaStream_t s,
+    Args... args)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return false;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        attr_done[dev] = true;
+    }
+    return strip_launch(kernel, grid, NT, smem, s, args...);
+}
+
+#define PSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
+    if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv) {                                              \
+        static bool done[64] = { false };                                                                   \
+        return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, y, mu, rstd, x, gamma, beta, \
+            plan.g, eps, (int)grid);                                                                        \
+    }
+#define PSTRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
+    if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
+        static bool done[64] = { false };                                                                   \
+        return pstrip_launch(gn_bwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, dx, sc.partials,       \
+            sc.tickets, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, plan.g, B, (int)grid);                 \
+    }
 
 #define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
@@ -944,6 +974,18 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
         const long grid = (long)B * plan.g.nct;
         if (grid > 2147483647L)
             return false;
+        {
+            // CTAs per SM: two 512-thread CTAs at 64 registers, or one at 128 registers (no spills)
+            int per_sm = plan.NT <= 256 ? 4 : (plan.NT <= 512 ? tune_get("gn_fwd_pstrip_ctas", 2) : 1);
+            const long resident = (long)sm_count() * per_sm;
+            const size_t psmem = (size_t)plan.VPT * plan.NT * 16 + plan.smem;
+            if (!tune_get("gn_no_pipeline", 0) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
+                const long pgrid = resident;
+                PSTRIP_FWD_CASE(1024, 4, 1) PSTRIP_FWD_CASE(1024, 8, 1)
+                PSTRIP_FWD_CASE(512, 4, 2) PSTRIP_FWD_CASE(512, 8, 2) PSTRIP_FWD_CASE(512, 8, 1)
+                PSTRIP_FWD_CASE(256, 4, 4) PSTRIP_FWD_CASE(256, 8, 4)
+            }
+        }
         STRIP_FWD_CASE(1024, 2) STRIP_FWD_CASE(1024, 4) STRIP_FWD_CASE(1024, 8)
         STRIP_FWD_CASE(512, 2) STRIP_FWD_CASE(512, 4) STRIP_FWD_CASE(512, 8)
         STRIP_FWD_CASE(256, 2) STRIP_FWD_CASE(256, 4) STRIP_FWD_CASE(256, 8)
@@ -979,6 +1021,18 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
         Scratch sc;
         if (!scratch_get(s, (size_t)2 * B * C, (size_t)plan.g.nct, &sc))
             return false;
+        {
+            const int per_sm = (plan.VPT == 8 || plan.NT == 1024) ? 1 : (plan.NT <= 256 ? 2 : 1);
+            const long resident = (long)sm_count() * per_sm;
+            const size_t psmem = (size_t)2 * plan.VPT * plan.NT * 16 + plan.smem;
+            // measured on B200: prefetching does not pay for the backward pass (one CTA per SM either
+            // way, 246 vs 236 us on [256,32,32,256]), so it is only taken on request
+            if (tune_get("gn_bwd_pipeline", 0) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
+                const long pgrid = resident;
+                PSTRIP_BWD_CASE(1024, 4, 1) PSTRIP_BWD_CASE(512, 4, 1) PSTRIP_BWD_CASE(512, 8, 1)
+                PSTRIP_BWD_CASE(256, 4, 2)
+            }
+        }
         STRIP_BWD_CASE(1024, 2, 1) STRIP_BWD_CASE(1024, 4, 1)
         STRIP_BWD_CASE(512, 2, 2) STRIP_BWD_CASE(512, 4, 2) STRIP_BWD_CASE(512, 8, 1)
         STRIP_BWD_CASE(256, 2, 4) STRIP_BWD_CASE(256, 4, 4)

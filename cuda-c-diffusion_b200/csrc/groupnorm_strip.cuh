@@ -316,4 +316,273 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
     }
 }
 
+
+// ===========================================================================
+// Pipelined strips: persistent CTAs that prefetch the NEXT strip with cp.async
+// ===========================================================================
+// Same register-resident processing as above, but a CTA loops over strips and, while it reduces,
+// normalises and stores strip i from registers, the 16-byte asynchronous copies of strip i+1 are
+// already in flight into shared memory.  Every thread stages exactly the float4 slots it will later
+// read itself (slot j of thread t lives at stage[j*NT + t]), so the staging needs no barrier at all:
+// a thread waits for its own copy group, moves its slots to registers and immediately re-arms them
+// with the copies of the following strip.  Each SM therefore always has a full strip (64-128 KB) of
+// loads outstanding, also during the barrier- and arithmetic-heavy phases.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int NT, int VPT, int NTENS>
+__device__ __forceinline__ void strip_prefetch(float4* stage, const StripGeom& g, int item, int q, int rl,
+    const float* __restrict__ t0, const float* __restrict__ t1)
+{
+    const int ctile = item % g.nct, b = item / g.nct;
+    const size_t base = (size_t)b * g.HW * g.C + (size_t)ctile * g.Ct + 4 * q;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int r = rl + j * g.RSTEP;
+        if (r < g.HW) {
+            cp_async16(&stage[j * NT + threadIdx.x], t0 + base + (size_t)r * g.C);
+            if (NTENS == 2)
+                cp_async16(&stage[(VPT + j) * NT + threadIdx.x], t1 + base + (size_t)r * g.C);
+        }
+    }
+    cp_async_commit();
+}
+
+// grid = min(items, resident CTAs), block = NT; dynamic smem = stage | red | chan | gstat
+template <int NT, int VPT, int ACT, int MB>
+__global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
+    float* __restrict__ mu, float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
+{
+    extern __shared__ float4 strip_stage[];
+    float4* stage = strip_stage;
+    float* red = reinterpret_cast<float*>(stage + VPT * NT);
+    const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * (NT / 32) * g.Ct : 2 * NT * 4;
+    float* chan = red + red_floats;
+    float* gstat = chan + 2 * g.Ct;
+    const int t = threadIdx.x;
+    const int q = t % g.Q, rl = t / g.Q;
+    const int cb = 4 * q;
+    const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
+
+    int item = blockIdx.x;
+    if (item < nitems)
+        strip_prefetch<NT, VPT, 1>(stage, g, item, q, rl, x, nullptr);
+    for (; item < nitems; item += gridDim.x) {
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
+        const float4 K = __ldg(reinterpret_cast<const float4*>(x + base));
+        cp_async_wait_all();
+        float4 v[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            v[j] = stage[j * NT + t];
+            if (rl + j * g.RSTEP >= g.HW)
+                v[j] = K;
+        }
+        if (item + (int)gridDim.x < nitems)
+            strip_prefetch<NT, VPT, 1>(stage, g, item + gridDim.x, q, rl, x, nullptr);
+
+        float4 s1 = make_float4(0.f, 0.f, 0.f, 0.f), s2 = s1;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const float d0 = v[j].x - K.x, d1 = v[j].y - K.y, d2 = v[j].z - K.z, d3 = v[j].w - K.w;
+            s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
+            s2.x = fmaf(d0, d0, s2.x); s2.y = fmaf(d1, d1, s2.y); s2.z = fmaf(d2, d2, s2.z); s2.w = fmaf(d3, d3, s2.w);
+        }
+        strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, s1, s2);
+        if (t < g.Gt) {
+            const float n = (float)g.HW * (float)g.cpg;
+            const float* xrow0 = x + (size_t)b * g.HW * g.C + c0 + t * g.cpg;
+            float msum = 0.0f;
+            for (int cl = 0; cl < g.cpg; ++cl)
+                msum += chan[t * g.cpg + cl] + (float)g.HW * __ldg(xrow0 + cl);
+            const float mean = msum / n;
+            float m2 = 0.0f;
+            for (int cl = 0; cl < g.cpg; ++cl) {
+                const int ch = t * g.cpg + cl;
+                const float dk = __ldg(xrow0 + cl) - mean;
+                m2 += chan[g.Ct + ch] + 2.0f * dk * chan[ch] + (float)g.HW * dk * dk;
+            }
+            const float rs = rsqrtf(m2 / n + eps);
+            gstat[t] = mean;
+            gstat[g.Gt + t] = rs;
+            mu[b * g.G + c0 / g.cpg + t] = mean;
+            rstd[b * g.G + c0 / g.cpg + t] = rs;
+        }
+        __syncthreads();
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+        const float4 be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+        float4 sc, sh;
+        sc.x = ga.x * gstat[g.Gt + g0]; sh.x = be.x - gstat[g0] * sc.x;
+        sc.y = ga.y * gstat[g.Gt + g1]; sh.y = be.y - gstat[g1] * sc.y;
+        sc.z = ga.z * gstat[g.Gt + g2]; sh.z = be.z - gstat[g2] * sc.z;
+        sc.w = ga.w * gstat[g.Gt + g3]; sh.w = be.w - gstat[g3] * sc.w;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int r = rl + j * g.RSTEP;
+            if (r < g.HW) {
+                float4 o;
+                o.x = act_value<ACT>(fmaf(v[j].x, sc.x, sh.x));
+                o.y = act_value<ACT>(fmaf(v[j].y, sc.y, sh.y));
+                o.z = act_value<ACT>(fmaf(v[j].z, sc.z, sh.z));
+                o.w = act_value<ACT>(fmaf(v[j].w, sc.w, sh.w));
+                __stcs(reinterpret_cast<float4*>(y + base + (size_t)r * g.C), o);
+            }
+        }
+    }
+}
+
+// backward: stage holds x (slots 0..VPT-1) and dy (slots VPT..2*VPT-1)
+template <int NT, int VPT, int ACT, int MB>
+__global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, float* __restrict__ partials,
+    unsigned int* __restrict__ tickets, float* __restrict__ dgamma, float* __restrict__ dbeta,
+    const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
+    const int B, const int nitems)
+{
+    extern __shared__ float4 strip_stage[];
+    __shared__ int s_is_last;
+    constexpr int NW = NT / 32;
+    float4* stage = strip_stage;
+    float* red = reinterpret_cast<float*>(stage + 2 * VPT * NT);
+    const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * NW * g.Ct : 2 * NT * 4;
+    float* chan = red + red_floats;
+    float* gstat = chan + 2 * g.Ct;
+    const int t = threadIdx.x;
+    const int q = t % g.Q, rl = t / g.Q;
+    const int cb = 4 * q;
+    const int gl0 = (cb + 0) / g.cpg, gl1 = (cb + 1) / g.cpg, gl2 = (cb + 2) / g.cpg, gl3 = (cb + 3) / g.cpg;
+
+    int item = blockIdx.x;
+    if (item < nitems)
+        strip_prefetch<NT, VPT, 2>(stage, g, item, q, rl, x, dy);
+    for (; item < nitems; item += gridDim.x) {
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
+        float4 be = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ACT != ACT_IDENTITY)
+            be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
+        const int gbase = b * g.G + c0 / g.cpg;
+        float4 rs4, nm4;
+        rs4.x = __ldg(rstd + gbase + gl0); nm4.x = -__ldg(mu + gbase + gl0) * rs4.x;
+        rs4.y = __ldg(rstd + gbase + gl1); nm4.y = -__ldg(mu + gbase + gl1) * rs4.y;
+        rs4.z = __ldg(rstd + gbase + gl2); nm4.z = -__ldg(mu + gbase + gl2) * rs4.z;
+        rs4.w = __ldg(rstd + gbase + gl3); nm4.w = -__ldg(mu + gbase + gl3) * rs4.w;
+
+        cp_async_wait_all();
+        float4 xv[VPT], dv[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            xv[j] = stage[j * NT + t];
+            dv[j] = stage[(VPT + j) * NT + t];
+        }
+        if (item + (int)gridDim.x < nitems)
+            strip_prefetch<NT, VPT, 2>(stage, g, item + gridDim.x, q, rl, x, dy);
+
+        float4 sA = make_float4(0.f, 0.f, 0.f, 0.f), sB = sA;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (rl + j * g.RSTEP < g.HW) {
+                xv[j].x = fmaf(xv[j].x, rs4.x, nm4.x);
+                xv[j].y = fmaf(xv[j].y, rs4.y, nm4.y);
+                xv[j].z = fmaf(xv[j].z, rs4.z, nm4.z);
+                xv[j].w = fmaf(xv[j].w, rs4.w, nm4.w);
+                if (ACT != ACT_IDENTITY) {
+                    dv[j].x *= act_slope<ACT>(fmaf(ga.x, xv[j].x, be.x));
+                    dv[j].y *= act_slope<ACT>(fmaf(ga.y, xv[j].y, be.y));
+                    dv[j].z *= act_slope<ACT>(fmaf(ga.z, xv[j].z, be.z));
+                    dv[j].w *= act_slope<ACT>(fmaf(ga.w, xv[j].w, be.w));
+                }
+                sA.x += dv[j].x; sA.y += dv[j].y; sA.z += dv[j].z; sA.w += dv[j].w;
+                sB.x = fmaf(dv[j].x, xv[j].x, sB.x); sB.y = fmaf(dv[j].y, xv[j].y, sB.y);
+                sB.z = fmaf(dv[j].z, xv[j].z, sB.z); sB.w = fmaf(dv[j].w, xv[j].w, sB.w);
+            }
+        }
+        strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, sA, sB);
+        if (t < g.Gt) {
+            float sg = 0.0f, sgx = 0.0f;
+            for (int cl = 0; cl < g.cpg; ++cl) {
+                const int ch = t * g.cpg + cl;
+                const float gm = __ldg(gamma + c0 + ch);
+                sg = fmaf(gm, chan[ch], sg);
+                sgx = fmaf(gm, chan[g.Ct + ch], sgx);
+            }
+            const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
+            gstat[t] = sg * inv_n;
+            gstat[g.Gt + t] = sgx * inv_n;
+        }
+        if (t < g.Ct) {
+            float* dst = partials + ((size_t)ctile * B + b) * (2 * g.Ct);
+            dst[t] = chan[g.Ct + t];
+            dst[g.Ct + t] = chan[t];
+        }
+        __syncthreads();
+        float4 mg, mgx;
+        mg.x = gstat[gl0]; mgx.x = gstat[g.Gt + gl0];
+        mg.y = gstat[gl1]; mgx.y = gstat[g.Gt + gl1];
+        mg.z = gstat[gl2]; mgx.z = gstat[g.Gt + gl2];
+        mg.w = gstat[gl3]; mgx.w = gstat[g.Gt + gl3];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int r = rl + j * g.RSTEP;
+            if (r < g.HW) {
+                float4 o;
+                o.x = rs4.x * (fmaf(dv[j].x, ga.x, -mg.x) - xv[j].x * mgx.x);
+                o.y = rs4.y * (fmaf(dv[j].y, ga.y, -mg.y) - xv[j].y * mgx.y);
+                o.z = rs4.z * (fmaf(dv[j].z, ga.z, -mg.z) - xv[j].z * mgx.z);
+                o.w = rs4.w * (fmaf(dv[j].w, ga.w, -mg.w) - xv[j].w * mgx.w);
+                __stcs(reinterpret_cast<float4*>(dx + base + (size_t)r * g.C), o);
+            }
+        }
+        // ---- ticket: the last sample of this channel tile folds the B partial rows
+        __threadfence();
+        __syncthreads();
+        if (t == 0) {
+            const unsigned old = atomicAdd(&tickets[ctile], 1u);
+            s_is_last = (old == (unsigned)B - 1u);
+        }
+        __syncthreads();
+        if (s_is_last) {
+            __threadfence();
+            const int width = 2 * g.Ct;
+            const int nq = width / 4;
+            int lanes = NT / nq;
+            const int cap = red_floats / width;
+            if (lanes > cap)
+                lanes = cap;
+            const int qi = t % nq, bl = t / nq;
+            const float* src = partials + (size_t)ctile * B * width;
+            if (bl < lanes) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int bb = bl; bb < B; bb += lanes) {
+                    const float4 p = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
+                    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+                }
+                reinterpret_cast<float4*>(red)[bl * nq + qi] = acc;
+            }
+            __syncthreads();
+            for (int j = t; j < width; j += NT) {
+                float s = 0.0f;
+                for (int r = 0; r < lanes; ++r)
+                    s += red[r * width + j];
+                if (j < g.Ct)
+                    dgamma[c0 + j] = s;
+                else
+                    dbeta[c0 + j - g.Ct] = s;
+            }
+            if (t == 0)
+                tickets[ctile] = 0;
+            __syncthreads();
+        }
+    }
+}
+
 }  // namespace b200

@@ -250,24 +250,28 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
     finally:
         for key in STRIP_KEYS + (b"gn_no_tile",):
             lib.b200_tune_set(key, 0)
-        lib.b200_tune_set(b"gn_bwd_strip_vpt", 4)
+        lib.b200_tune_set(b"gn_bwd_strip_vpt", 8)
     _check(got, ref, f"strip nt{nt}")
 
 
-def test_groupnorm_strip_stagger_many_ctas(lib, orc):
-    """More strips than one wave of CTAs, so the staggered start of the second CTA per SM is exercised."""
-    p = dict(B=160, HW=64, C=32, G=8, act="silu")
+@pytest.mark.parametrize("bwd_pipeline", [0, 1])
+def test_groupnorm_pipelined_strips(lib, orc, bwd_pipeline):
+    """Many more strips than resident CTAs: the persistent kernels that prefetch the next strip with
+    cp.async are taken (forward by default, backward on request) and loop several times."""
+    p = dict(B=320, HW=1024, C=32, G=8, act="silu")
+    lib.b200_tune_set(b"gn_bwd_pipeline", bwd_pipeline)
     inp = cases.make_inputs("groupnorm", p, seed=37)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    for key, val in ((b"gn_fwd_strip_ct", 8), (b"gn_bwd_strip_ct", 8), (b"gn_fwd_strip_nt", 512), (b"gn_bwd_strip_nt", 512)):
-        lib.b200_tune_set(key, val)
     try:
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+        got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
-        for key in STRIP_KEYS:
+        for key in STRIP_KEYS + (b"gn_bwd_pipeline",):
             lib.b200_tune_set(key, 0)
-        lib.b200_tune_set(b"gn_bwd_strip_vpt", 4)
-    _check(got, ref, "stagger")
+        lib.b200_tune_set(b"gn_bwd_strip_vpt", 8)
+    _check(got, ref, "pipelined")
+    for k in got:
+        assert np.array_equal(got[k], got2[k]), k
 
 
 def test_multi_tensor_entry_points(pkg, lib, orc):
