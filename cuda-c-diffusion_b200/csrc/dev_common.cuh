@@ -163,9 +163,22 @@ __device__ __forceinline__ float rational_tanh(float x)
 // (tanh(x/2)+1)/2.  The reference clamps the result to [0,1] once more; with the
 // tanh already clamped to [-1,1] that second clamp can never change the value
 // ((t+1)*0.5 is exact at both ends and monotone), so it is not repeated here.
+//
+// tanh(x/2) is evaluated directly in x: with h = x/2 every coefficient below is
+// the reference's coefficient times a power of two (135135/4, 17325/16, 378/64,
+// 1/256 for the numerator; 135135/2, 62370/8, 3150/32, 28/128 for the
+// denominator), all exactly representable, so each intermediate is the
+// reference's intermediate scaled by a power of two and the quotient is
+// bit-identical to rational_tanh(x * 0.5f) -- one multiply cheaper.
 __device__ __forceinline__ float rational_sigmoid(float x)
 {
-    return (rational_tanh(x * 0.5f) + 1.0f) * 0.5f;
+    const float x2 = x * x;
+    const float num = x * (33783.75f + x2 * (1082.8125f + x2 * (5.90625f + x2 * 0.00390625f)));
+    const float den = 67567.5f + x2 * (7796.25f + x2 * (98.4375f + x2 * 0.21875f));
+    float rden;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rden) : "f"(den));
+    const float t = fmaxf(-1.0f, fminf(1.0f, num * rden));
+    return fmaf(t, 0.5f, 0.5f);
 }
 
 #define B200_MP_SILU_SCALE (1.0f / 0.596f)

@@ -827,6 +827,9 @@ static bool gn_forward_tile(float* y, float* mu, float* rstd, const float* x, co
 // ---------------------------------------------------------------------------
 // strip (register-resident) dispatch
 // ---------------------------------------------------------------------------
+void fold_partials(float* out_a, float* out_b, const float* partials, int nparts, int width, int split,
+    cudaStream_t s);  // rownorm.cu
+
 struct StripPlan {
     int NT, VPT;
     StripGeom g;
@@ -938,14 +941,20 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
 #define PSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv) {                                              \
         static bool done[64] = { false };                                                                   \
-        return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, y, mu, rstd, x, gamma, beta, \
-            plan.g, eps, (int)grid);                                                                        \
+        if (full) {                                                                                         \
+            static bool donef[64] = { false };                                                              \
+            return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, psmem, s, y, mu, rstd, x, \
+                gamma, beta, plan.g, eps, (int)grid);                                                       \
+        }                                                                                                   \
+        return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, psmem, s, y, mu, rstd, x, \
+            gamma, beta, plan.g, eps, (int)grid);                                                           \
     }
 #define PSTRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
         static bool done[64] = { false };                                                                   \
         return pstrip_launch(gn_bwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, dx, sc.partials,       \
-            sc.tickets, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, plan.g, B, (int)grid);                 \
+                   dy, x, gamma, beta, mu, rstd, plan.g, (int)grid)                                         \
+            && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);                           \
     }
 
 #define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
@@ -955,7 +964,8 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
 #define STRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
         return strip_launch(gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, plan.smem, s, dx, sc.partials,  \
-            sc.tickets, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, plan.g, B);
+                   dy, x, gamma, beta, mu, rstd, plan.g, B)                                                \
+            && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
 
 template <int ACT>
 static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, const float* gamma,
@@ -981,6 +991,7 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
             const size_t psmem = (size_t)plan.VPT * plan.NT * 16 + plan.smem;
             if (!tune_get("gn_no_pipeline", 0) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
                 const long pgrid = resident;
+                const bool full = plan.g.RSTEP * plan.VPT == HW;
                 PSTRIP_FWD_CASE(1024, 4, 1) PSTRIP_FWD_CASE(1024, 8, 1)
                 PSTRIP_FWD_CASE(512, 4, 2) PSTRIP_FWD_CASE(512, 8, 2) PSTRIP_FWD_CASE(512, 8, 1)
                 PSTRIP_FWD_CASE(256, 4, 4) PSTRIP_FWD_CASE(256, 8, 4)
@@ -1019,15 +1030,13 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
         if (grid > 2147483647L)
             return false;
         Scratch sc;
-        if (!scratch_get(s, (size_t)2 * B * C, (size_t)plan.g.nct, &sc))
+        if (!scratch_get(s, (size_t)2 * B * C, 0, &sc))
             return false;
         {
             const int per_sm = (plan.VPT == 8 || plan.NT == 1024) ? 1 : (plan.NT <= 256 ? 2 : 1);
             const long resident = (long)sm_count() * per_sm;
             const size_t psmem = (size_t)2 * plan.VPT * plan.NT * 16 + plan.smem;
-            // measured on B200: prefetching does not pay for the backward pass (one CTA per SM either
-            // way, 246 vs 236 us on [256,32,32,256]), so it is only taken on request
-            if (tune_get("gn_bwd_pipeline", 0) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
+            if (tune_get("gn_bwd_pipeline", 1) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
                 const long pgrid = resident;
                 PSTRIP_BWD_CASE(1024, 4, 1) PSTRIP_BWD_CASE(512, 4, 1) PSTRIP_BWD_CASE(512, 8, 1)
                 PSTRIP_BWD_CASE(256, 4, 2)

@@ -165,18 +165,18 @@ __global__ void __launch_bounds__(NT, (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))) gn_
 
 // ---------------------------------------------------------------------------
 // backward: grid = B * nct, block = NT
-// partials layout: [nct][B][2*Ct] (first Ct: dgamma, next Ct: dbeta); the last CTA of
-// a channel tile (atomic ticket) adds the B rows in a fixed order.
+// Per-sample partial rows of the parameter gradients go to partials[b][2*C] (first C: dgamma,
+// next C: dbeta); a small fold kernel launched right after adds the B rows in a fixed order.
+// (A last-CTA ticket inside this kernel was measured: its fence + atomic round trip sits on
+// every strip's critical path and costs far more than the extra 4-7 us launch.)
 // ---------------------------------------------------------------------------
 template <int NT, int VPT, int ACT, int MB>
 __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
-    float* __restrict__ partials, unsigned int* __restrict__ tickets, float* __restrict__ dgamma,
-    float* __restrict__ dbeta, const float* __restrict__ dy, const float* __restrict__ x,
+    float* __restrict__ partials, const float* __restrict__ dy, const float* __restrict__ x,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mu,
     const float* __restrict__ rstd, const StripGeom g, const int B)
 {
     extern __shared__ float strip_smem[];
-    __shared__ int s_is_last;
     constexpr int NW = NT / 32;
     float* red = strip_smem;
     const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * NW * g.Ct : 2 * NT * 4;
@@ -249,10 +249,10 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
         gstat[t] = sg * inv_n;
         gstat[g.Gt + t] = sgx * inv_n;
     }
-    if (t < g.Ct) {
-        float* dst = partials + ((size_t)ctile * B + b) * (2 * g.Ct);
-        dst[t] = chan[g.Ct + t];
-        dst[g.Ct + t] = chan[t];
+    if (t < g.Ct) {  // one partial row per sample: [b][0:C] dgamma, [b][C:2C] dbeta
+        float* dst = partials + (size_t)b * (2 * g.C) + c0 + t;
+        dst[0] = chan[g.Ct + t];
+        dst[g.C] = chan[t];
     }
     __syncthreads();
 
@@ -274,48 +274,7 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
         }
     }
 
-    // ---- ticket: the last sample of this channel tile folds the B partial rows
-    __threadfence();
-    __syncthreads();
-    if (t == 0) {
-        const unsigned old = atomicAdd(&tickets[ctile], 1u);
-        s_is_last = (old == (unsigned)B - 1u);
-    }
-    __syncthreads();
-    if (s_is_last) {
-        __threadfence();
-        const int nrows = B;
-        const int width = 2 * g.Ct;
-        const int nq = width / 4;
-        int lanes = NT / nq;
-        const int cap = red_floats / width;
-        if (lanes > cap)
-            lanes = cap;
-        const int qi = t % nq, bl = t / nq;
-        const float* src = partials + (size_t)ctile * nrows * width;
-        if (bl < lanes) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int bb = bl; bb < nrows; bb += lanes) {
-                const float4 p = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
-                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-            }
-            reinterpret_cast<float4*>(red)[bl * nq + qi] = acc;
-        }
-        __syncthreads();
-        for (int j = t; j < width; j += NT) {
-            float s = 0.0f;
-            for (int r = 0; r < lanes; ++r)
-                s += red[r * width + j];
-            if (j < g.Ct)
-                dgamma[c0 + j] = s;
-            else
-                dbeta[c0 + j - g.Ct] = s;
-        }
-        if (t == 0)
-            tickets[ctile] = 0;
-    }
 }
-
 
 // ===========================================================================
 // Pipelined strips: persistent CTAs that prefetch the NEXT strip with cp.async
@@ -353,7 +312,8 @@ __device__ __forceinline__ void strip_prefetch(float4* stage, const StripGeom& g
 }
 
 // grid = min(items, resident CTAs), block = NT; dynamic smem = stage | red | chan | gstat
-template <int NT, int VPT, int ACT, int MB>
+// FULL: HW == RSTEP * VPT, i.e. every register slot holds a real row and no row test is needed.
+template <int NT, int VPT, int ACT, int MB, bool FULL>
 __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
     float* __restrict__ mu, float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
@@ -372,8 +332,10 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
     int item = blockIdx.x;
     if (item < nitems)
         strip_prefetch<NT, VPT, 1>(stage, g, item, q, rl, x, nullptr);
+    // (ctile, b) of the current item, advanced incrementally (no division in the loop)
+    int ctile = item % g.nct, b = item / g.nct;
+    const int step_ct = (int)gridDim.x % g.nct, step_b = (int)gridDim.x / g.nct;
     for (; item < nitems; item += gridDim.x) {
-        const int ctile = item % g.nct, b = item / g.nct;
         const int c0 = ctile * g.Ct;
         const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
         const float4 K = __ldg(reinterpret_cast<const float4*>(x + base));
@@ -382,7 +344,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             v[j] = stage[j * NT + t];
-            if (rl + j * g.RSTEP >= g.HW)
+            if (!FULL && rl + j * g.RSTEP >= g.HW)
                 v[j] = K;
         }
         if (item + (int)gridDim.x < nitems)
@@ -416,6 +378,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
             rstd[b * g.G + c0 / g.cpg + t] = rs;
         }
         __syncthreads();
+        // (loading gamma/beta before the wait was measured: the 8 extra live registers spill and cost
+        // more than the L2 round trip they would hide)
         const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
         const float4 be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
         float4 sc, sh;
@@ -426,7 +390,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int r = rl + j * g.RSTEP;
-            if (r < g.HW) {
+            if (FULL || r < g.HW) {
                 float4 o;
                 o.x = act_value<ACT>(fmaf(v[j].x, sc.x, sh.x));
                 o.y = act_value<ACT>(fmaf(v[j].y, sc.y, sh.y));
@@ -435,19 +399,23 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
                 __stcs(reinterpret_cast<float4*>(y + base + (size_t)r * g.C), o);
             }
         }
+        ctile += step_ct;
+        b += step_b;
+        if (ctile >= g.nct) {
+            ctile -= g.nct;
+            ++b;
+        }
     }
 }
 
 // backward: stage holds x (slots 0..VPT-1) and dy (slots VPT..2*VPT-1)
 template <int NT, int VPT, int ACT, int MB>
 __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, float* __restrict__ partials,
-    unsigned int* __restrict__ tickets, float* __restrict__ dgamma, float* __restrict__ dbeta,
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
-    const int B, const int nitems)
+    const int nitems)
 {
     extern __shared__ float4 strip_stage[];
-    __shared__ int s_is_last;
     constexpr int NW = NT / 32;
     float4* stage = strip_stage;
     float* red = reinterpret_cast<float*>(stage + 2 * VPT * NT);
@@ -462,8 +430,9 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
     int item = blockIdx.x;
     if (item < nitems)
         strip_prefetch<NT, VPT, 2>(stage, g, item, q, rl, x, dy);
+    int ctile = item % g.nct, b = item / g.nct;
+    const int step_ct = (int)gridDim.x % g.nct, step_b = (int)gridDim.x / g.nct;
     for (; item < nitems; item += gridDim.x) {
-        const int ctile = item % g.nct, b = item / g.nct;
         const int c0 = ctile * g.Ct;
         const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
         const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
@@ -519,10 +488,10 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
             gstat[t] = sg * inv_n;
             gstat[g.Gt + t] = sgx * inv_n;
         }
-        if (t < g.Ct) {
-            float* dst = partials + ((size_t)ctile * B + b) * (2 * g.Ct);
-            dst[t] = chan[g.Ct + t];
-            dst[g.Ct + t] = chan[t];
+        if (t < g.Ct) {  // one partial row per sample: [b][0:C] dgamma, [b][C:2C] dbeta
+            float* dst = partials + (size_t)b * (2 * g.C) + c0 + t;
+            dst[0] = chan[g.Ct + t];
+            dst[g.C] = chan[t];
         }
         __syncthreads();
         float4 mg, mgx;
@@ -542,45 +511,11 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
                 __stcs(reinterpret_cast<float4*>(dx + base + (size_t)r * g.C), o);
             }
         }
-        // ---- ticket: the last sample of this channel tile folds the B partial rows
-        __threadfence();
-        __syncthreads();
-        if (t == 0) {
-            const unsigned old = atomicAdd(&tickets[ctile], 1u);
-            s_is_last = (old == (unsigned)B - 1u);
-        }
-        __syncthreads();
-        if (s_is_last) {
-            __threadfence();
-            const int width = 2 * g.Ct;
-            const int nq = width / 4;
-            int lanes = NT / nq;
-            const int cap = red_floats / width;
-            if (lanes > cap)
-                lanes = cap;
-            const int qi = t % nq, bl = t / nq;
-            const float* src = partials + (size_t)ctile * B * width;
-            if (bl < lanes) {
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int bb = bl; bb < B; bb += lanes) {
-                    const float4 p = __ldcg(reinterpret_cast<const float4*>(src + (size_t)bb * width) + qi);
-                    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-                }
-                reinterpret_cast<float4*>(red)[bl * nq + qi] = acc;
-            }
-            __syncthreads();
-            for (int j = t; j < width; j += NT) {
-                float s = 0.0f;
-                for (int r = 0; r < lanes; ++r)
-                    s += red[r * width + j];
-                if (j < g.Ct)
-                    dgamma[c0 + j] = s;
-                else
-                    dbeta[c0 + j - g.Ct] = s;
-            }
-            if (t == 0)
-                tickets[ctile] = 0;
-            __syncthreads();
+        ctile += step_ct;
+        b += step_b;
+        if (ctile >= g.nct) {
+            ctile -= g.nct;
+            ++b;
         }
     }
 }

@@ -246,7 +246,7 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
     try:
         n0 = lib.b200_launch_count()
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
-        assert lib.b200_launch_count() - n0 == 2, "expected one forward and one backward strip kernel"
+        assert lib.b200_launch_count() - n0 == 3, "expected the forward strip, backward strip and fold kernels"
     finally:
         for key in STRIP_KEYS + (b"gn_no_tile",):
             lib.b200_tune_set(key, 0)
@@ -259,16 +259,17 @@ def test_groupnorm_pipelined_strips(lib, orc, bwd_pipeline):
     """Many more strips than resident CTAs: the persistent kernels that prefetch the next strip with
     cp.async are taken (forward by default, backward on request) and loop several times."""
     p = dict(B=320, HW=1024, C=32, G=8, act="silu")
-    lib.b200_tune_set(b"gn_bwd_pipeline", bwd_pipeline)
+    lib.b200_tune_set(b"gn_bwd_pipeline", bwd_pipeline)  # 0 = plain strips
     inp = cases.make_inputs("groupnorm", p, seed=37)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
     try:
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
         got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
-        for key in STRIP_KEYS + (b"gn_bwd_pipeline",):
+        for key in STRIP_KEYS:
             lib.b200_tune_set(key, 0)
         lib.b200_tune_set(b"gn_bwd_strip_vpt", 8)
+        lib.b200_tune_set(b"gn_bwd_pipeline", 1)
     _check(got, ref, "pipelined")
     for k in got:
         assert np.array_equal(got[k], got2[k]), k
