@@ -989,8 +989,10 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
             int per_sm = plan.NT <= 256 ? 4 : (plan.NT <= 512 ? tune_get("gn_fwd_pstrip_ctas", 2) : 1);
             const long resident = (long)sm_count() * per_sm;
             const size_t psmem = (size_t)plan.VPT * plan.NT * 16 + plan.smem;
-            if (!tune_get("gn_no_pipeline", 0) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
-                const long pgrid = resident;
+            if (!tune_get("gn_no_pipeline", 0) && grid > resident && psmem * per_sm <= 220 * 1024) {
+                // even share: every CTA gets (almost) the same number of strips
+                const long per_cta = (grid + resident - 1) / resident;
+                const long pgrid = (grid + per_cta - 1) / per_cta;
                 const bool full = plan.g.RSTEP * plan.VPT == HW;
                 PSTRIP_FWD_CASE(1024, 4, 1) PSTRIP_FWD_CASE(1024, 8, 1)
                 PSTRIP_FWD_CASE(512, 4, 2) PSTRIP_FWD_CASE(512, 8, 2) PSTRIP_FWD_CASE(512, 8, 1)
@@ -1036,8 +1038,10 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
             const int per_sm = (plan.VPT == 8 || plan.NT == 1024) ? 1 : (plan.NT <= 256 ? 2 : 1);
             const long resident = (long)sm_count() * per_sm;
             const size_t psmem = (size_t)2 * plan.VPT * plan.NT * 16 + plan.smem;
-            if (tune_get("gn_bwd_pipeline", 1) && grid >= 2 * resident && psmem * per_sm <= 220 * 1024) {
-                const long pgrid = resident;
+            if (tune_get("gn_bwd_pipeline", 1) && grid > resident && psmem * per_sm <= 220 * 1024) {
+                // even share: every CTA gets (almost) the same number of strips
+                const long per_cta = (grid + resident - 1) / resident;
+                const long pgrid = (grid + per_cta - 1) / per_cta;
                 PSTRIP_BWD_CASE(1024, 4, 1) PSTRIP_BWD_CASE(512, 4, 1) PSTRIP_BWD_CASE(512, 8, 1)
                 PSTRIP_BWD_CASE(256, 4, 2)
             }
