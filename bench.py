@@ -425,6 +425,43 @@ def cpu_baseline(threads=None, samples=16, min_seconds=8.0):
                       f"plain-C port of its kernels"}
 
 
+# ------------------------------------------------------------------------------------ range-sharded optimizer
+def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10):
+    """Optimizer config: flat 64M-parameter vector, fused Adam+EMA on this rank's parameter range, then an
+    in-place NCCL all-gather of the updated parameters.  Returns per-GPU kernel GB/s (36 B/param of the
+    local range) and the time of update+gather."""
+    sh = importlib.import_module("cuda-c-diffusion_b200.sharding")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(7)  # same seed everywhere: replicated parameters
+    p = 0.02 * torch.randn(npar, device=dev, generator=g)
+    grad = 1e-3 * torch.randn(npar, device=dev, generator=g)
+    opt = sh.ShardedAdamEMA(p, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, decay=0.999)
+    for _ in range(3):
+        opt.step(grad, grad_scale=1.0 / world)
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_kernel = t_total = 0.0
+    for _ in range(iters):
+        ev[0].record()
+        opt.step(grad, grad_scale=1.0 / world, gather=False)
+        ev[1].record()
+        opt.all_gather()
+        ev[2].record()
+        torch.cuda.synchronize()
+        t_kernel += ev[0].elapsed_time(ev[1])
+        t_total += ev[0].elapsed_time(ev[2])
+    t = torch.tensor([t_kernel / iters, t_total / iters], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    kern_ms, tot_ms = float(t[0]), float(t[1])
+    return {"params": npar, "shard": opt.shard, "kernel_ms": round(kern_ms, 4), "update_plus_allgather_ms": round(tot_ms, 4),
+            "kernel_GBps_per_gpu": round(36 * opt.shard / (kern_ms * 1e-3) / 1e9, 1),
+            "allgather_GBps_per_gpu_in": round((world - 1) * opt.shard * 4 / max((tot_ms - kern_ms) * 1e-3, 1e-9) / 1e9, 1)
+            if world > 1 else None}
+
+
 # ------------------------------------------------------------------------------------ EDM UNet training step
 def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
     """Images/s of the reference's own EDM trainer (edm/main_edm.c + diffusion/train.c + every host module,
@@ -569,11 +606,16 @@ def main():
     else:
         line["impl"] = "reference"
         line["reference_kind"] = ref_note
+    if args.impl == "b200" and not args.no_ops:
+        del step
+        torch.cuda.empty_cache()
+        step = None
+        line["sharded_adam_ema"] = sharded_adam_ema(lib, world, rank)
     if rank == 0:
         if not args.no_cpu and (world == 1 or args.impl == "reference"):
             line["cpu_baseline"] = cpu_baseline()
         if not args.no_ops and world == 1:
-            del step
+            step = None
             torch.cuda.empty_cache()
             line["ops"] = ops_table(lib_run, fused, peak)
             exe = ROOT / "oracle" / "_ref" / ("edm_demo_b200" if args.impl == "b200" else "edm_demo_ref")
