@@ -23,6 +23,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -124,11 +125,9 @@ class ShardedAdamEMA:
         return self.params[self.lo:self.hi]
 
     def hyper(self, grad_scale=1.0) -> AdamHyper:
-        b1 = torch.tensor(self.beta1, dtype=torch.float32)
-        b2 = torch.tensor(self.beta2, dtype=torch.float32)
-        tt = torch.tensor(float(self.t), dtype=torch.float32)
-        bc1 = float(1.0 - torch.pow(b1, tt))
-        bc2 = float(1.0 - torch.pow(b2, tt))
+        tt = np.float32(self.t)
+        bc1 = float(np.float32(1.0) - np.power(np.float32(self.beta1), tt))
+        bc2 = float(np.float32(1.0) - np.power(np.float32(self.beta2), tt))
         return AdamHyper(self.lr, self.beta1, self.beta2, self.eps, bc1, bc2, self.decay, grad_scale)
 
     def step(self, grads: torch.Tensor, grad_scale: float = 1.0, gather: bool = True) -> None:
