@@ -463,6 +463,24 @@ def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10):
 
 
 # ------------------------------------------------------------------------------------ EDM UNet training step
+def write_edm_config(folder, batch, train_steps):
+    """Writes the synthetic image file and an .ini for the reference's EDM trainer into `folder`; returns the
+    .ini path.  Also reachable as `bench.py --write-edm-config FOLDER` for profiler captures of the trainer."""
+    os.makedirs(folder, exist_ok=True)
+    images = os.path.join(folder, "images.bin")
+    if not os.path.exists(images):
+        rng = np.random.default_rng(0)
+        n = 4096
+        img = np.where(rng.random((n, 28, 28)) < 0.8, -1.0, rng.uniform(-1, 1, (n, 28, 28))).astype(np.float32)
+        img.tofile(images)
+    ini = os.path.join(folder, f"edm_{train_steps}.ini")
+    with open(ini, "w") as f:
+        f.write(f"channels = 64,128,128\nemb_dim = 128\nheads = 1\nt = 0.3\nbatch_size = {batch}\n"
+                f"train_steps = {train_steps}\nlr = 1e-3\nlr_warmup = 500\nlr_ref = 5000\nema_decay = 0.999\n"
+                f"tf32 = 1\nsample_steps = 1\nvis_batch = 1\nimages = {images}\nH = 28\nW = 28\nC = 1\n")
+    return ini
+
+
 def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
     """Images/s of the reference's own EDM trainer (edm/main_edm.c + diffusion/train.c + every host module,
     unmodified) with the given kernel backend linked in.  Config: channels 64/128/128, emb 128, 1 head, t 0.3,
@@ -472,17 +490,9 @@ def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
     if not Path(binary).exists():
         return None
     with tempfile.TemporaryDirectory() as tmp:
-        rng = np.random.default_rng(0)
-        n = 4096
-        img = np.where(rng.random((n, 28, 28)) < 0.8, -1.0, rng.uniform(-1, 1, (n, 28, 28))).astype(np.float32)
-        img.tofile(os.path.join(tmp, "images.bin"))
         times = []
         for st in (2,) + tuple(steps):  # the first (2-step) run only warms caches and is not used
-            ini = os.path.join(tmp, f"edm_{st}.ini")
-            with open(ini, "w") as f:
-                f.write(f"channels = 64,128,128\nemb_dim = 128\nheads = 1\nt = 0.3\nbatch_size = {batch}\n"
-                        f"train_steps = {st}\nlr = 1e-3\nlr_warmup = 500\nlr_ref = 5000\nema_decay = 0.999\n"
-                        f"tf32 = 1\nsample_steps = 1\nvis_batch = 1\nimages = {tmp}/images.bin\nH = 28\nW = 28\nC = 1\n")
+            ini = write_edm_config(tmp, batch, st)
             t0 = time.perf_counter()
             res = subprocess.run([str(binary), ini], cwd=tmp, capture_output=True, text=True, timeout=900)
             times.append(time.perf_counter() - t0)
@@ -517,7 +527,13 @@ def main():
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
                     help="set a kernel tunable (b200_tune_set), e.g. gn_no_strip=1 to time the TMA tile kernels")
     ap.add_argument("--batch", type=int, default=256, help="samples per GPU; values other than 256 are for profiling only")
+    ap.add_argument("--write-edm-config", metavar="FOLDER", help="write images.bin + edm_<steps>.ini for the reference's "
+                    "EDM trainer (same config as the timing leg) and exit")
+    ap.add_argument("--edm-steps", type=int, default=6, help="train_steps for --write-edm-config")
     args = ap.parse_args()
+    if args.write_edm_config:
+        print(write_edm_config(args.write_edm_config, args.batch, args.edm_steps))
+        return
     if args.batch != 256:
         set_batch(args.batch)
     args.warmup = max(args.warmup, 3)

@@ -3,17 +3,26 @@
 // One CTA owns the strip [all HW rows of one sample] x [Ct channels covering
 // whole groups] and keeps it entirely in REGISTERS: thread t holds the float4
 // column q = t % Q (Q = Ct/4) of rows rl, rl+RSTEP, ... (RSTEP = NT/Q), VPT rows
-// in all.  Every load of the strip is issued before the first is consumed, so a
-// single CTA has its whole strip (up to 128 KB) in flight; statistics, the
-// normalised output (or dx) and the parameter-gradient partials are all computed
-// from registers, so x (and dy) cross HBM exactly once and nothing but a few
-// hundred floats of partial sums ever touches shared memory.  The CTA needs two
-// __syncthreads per strip and no cluster, no TMA descriptor and no staging
-// buffer; it is the GroupNorm analogue of the warp-per-row LayerNorm kernel.
+// in all.  Statistics, the normalised output (or dx) and the parameter-gradient
+// partials are all computed from registers, so x (and dy) cross HBM exactly once.
 //
-// The strip must fit the register file: HW <= RSTEP * VPT with VPT <= 8
-// (forward) or <= 4 per tensor (backward).  Larger samples take the TMA /
-// cluster tile kernels.
+// Two generations live here:
+//   gn_fwd_strip / gn_bwd_strip    one strip per CTA; every load of the strip is
+//                                  issued before the first is consumed.
+//   gn_fwd_pstrip / gn_bwd_pstrip  persistent and pipelined (the default): a CTA
+//                                  walks strips blockIdx.x, +gridDim.x, ... and,
+//                                  while it computes strip i from registers, its
+//                                  threads stage their own float4 slots of strip
+//                                  i+1 in shared memory with cp.async (each thread
+//                                  reads back only what it staged, so staging needs
+//                                  no barrier).  The HBM pipe therefore stays busy
+//                                  during the arithmetic and the stores.
+// The backward kernels write one dgamma/dbeta partial row per sample; a separate
+// fixed-order fold kernel (rownorm.cu: fold_partials) sums them, which keeps the
+// result deterministic and keeps fences and atomics off each strip's critical path.
+//
+// The strip must fit the register file: HW <= RSTEP * VPT with VPT <= 8 per
+// tensor.  Larger samples take the TMA / cluster tile kernels of groupnorm.cu.
 #pragma once
 
 namespace b200 {
