@@ -4,6 +4,7 @@
 // surface is include/b200_layer_kernels.h.
 #pragma once
 
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -48,8 +49,26 @@ void report_error(const char* file, int line, const char* fmt, ...);
     } while (0)
 
 int sm_count();              // SMs of the current device (cached per device)
-int tune_get(const char* key, int dflt);  // value set through b200_tune_set, else dflt
+int tune_lookup(const char* key, int dflt);  // value set through b200_tune_set, else dflt (locked map lookup)
+unsigned tune_generation();                    // bumped by every b200_tune_set
 void count_launch(int n = 1);  // increments the library's launch counter
+
+// Launchers read tunables on every call and some hosts issue thousands of tiny launches per
+// step, so each call site caches its value and re-reads the map only after a b200_tune_set.
+struct TuneSite {
+    std::atomic<unsigned> gen{ 0xffffffffu };
+    std::atomic<int> value{ 0 };
+    int get(const char* key, int dflt)
+    {
+        const unsigned g = tune_generation();
+        if (gen.load(std::memory_order_acquire) != g) {
+            value.store(tune_lookup(key, dflt), std::memory_order_relaxed);
+            gen.store(g, std::memory_order_release);
+        }
+        return value.load(std::memory_order_relaxed);
+    }
+};
+#define tune_get(key, dflt) ([&]() -> int { static ::b200::TuneSite site_; return site_.get(key, dflt); }())
 
 // Scratch memory owned by the library, one arena per (device, stream).  Grows
 // on demand (allocation happens only when a call needs more than is reserved);

@@ -433,10 +433,11 @@ __global__ void __launch_bounds__(RN_THREADS) pixelnorm_generic(float* __restric
 // ---------------------------------------------------------------------------
 // host dispatch
 // ---------------------------------------------------------------------------
+// (the key varies per caller, so this site uses the uncached lookup)
 static inline int rows_grid(long rows, int rows_per_block, const char* key, int dflt)
 {
     long want = (rows + rows_per_block - 1) / rows_per_block;
-    const long cap = (long)sm_count() * tune_get(key, dflt);
+    const long cap = (long)sm_count() * tune_lookup(key, dflt);
     if (want > cap)
         want = cap;
     return want < 1 ? 1 : (int)want;

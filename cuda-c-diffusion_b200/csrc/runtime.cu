@@ -3,6 +3,7 @@
 #include "dev_common.cuh"
 #include "../../include/b200_layer_kernels.h"
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <stdarg.h>
@@ -35,7 +36,8 @@ static int g_error_mode = 0;
 static int g_error_count = 0;
 static std::string g_last_error;
 static std::map<std::string, int> g_tunables;
-static long long g_launches = 0;
+static std::atomic<long long> g_launches{ 0 };
+static std::atomic<unsigned> g_tune_gen{ 0 };
 
 void report_error(const char* file, int line, const char* fmt, ...)
 {
@@ -75,18 +77,16 @@ int sm_count()
     return cached[dev];
 }
 
-int tune_get(const char* key, int dflt)
+int tune_lookup(const char* key, int dflt)
 {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_tunables.find(key);
     return it == g_tunables.end() ? dflt : it->second;
 }
 
-void count_launch(int n)
-{
-    std::lock_guard<std::mutex> lk(g_mu);
-    g_launches += n;
-}
+unsigned tune_generation() { return g_tune_gen.load(std::memory_order_acquire); }
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // --- scratch arenas ----------------------------------------------------------
 struct Arena {
@@ -176,17 +176,9 @@ int b200_device_error_status(void)
     return v;
 }
 
-long long b200_launch_count(void)
-{
-    std::lock_guard<std::mutex> lk(g_mu);
-    return g_launches;
-}
+long long b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-void b200_launch_count_reset(void)
-{
-    std::lock_guard<std::mutex> lk(g_mu);
-    g_launches = 0;
-}
+void b200_launch_count_reset(void) { g_launches.store(0, std::memory_order_relaxed); }
 
 int b200_scratch_reserve(cudaStream_t s, long long bytes)
 {
@@ -197,11 +189,14 @@ int b200_scratch_reserve(cudaStream_t s, long long bytes)
 
 void b200_tune_set(const char* key, int value)
 {
-    std::lock_guard<std::mutex> lk(g_mu);
-    g_tunables[key] = value;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_tunables[key] = value;
+    }
+    g_tune_gen.fetch_add(1, std::memory_order_release);
 }
 
-int b200_tune_get(const char* key, int dflt) { return tune_get(key, dflt); }
+int b200_tune_get(const char* key, int dflt) { return tune_lookup(key, dflt); }
 
 const char* b200_version(void) { return "b200-layer-kernels 0.1 (sm_100a)"; }
 
