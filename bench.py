@@ -504,6 +504,33 @@ def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
                 "steps_timed": nst, "how": "wall-clock difference of two runs of the unmodified reference trainer"}
 
 
+def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True):
+    """Data-parallel EDM UNet training (oracle/_ref/edm_dp_train: the reference's UNet and host modules, this
+    library's kernels, NCCL gradient all-reduce).  Every rank of this benchmark starts one trainer process on
+    its own GPU; the trainers find each other through a file named after MASTER_PORT.  Rank 0 returns the
+    trainer's JSON (device-timed, max over ranks), the other ranks None."""
+    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+    if not exe.exists():
+        return None
+    env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local_rank))
+    id_file = f"/tmp/edm_dp_train_{os.environ.get('MASTER_PORT', '0')}_{batch_per_gpu}.ncclid"
+    cmd = [str(exe), "--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup), "--id-file", id_file]
+    if graph:
+        cmd.append("--graph")
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        return {"error": "timeout"} if rank == 0 else None
+    if rank != 0:
+        return None
+    if res.returncode != 0:
+        return {"error": (res.stderr or res.stdout)[-300:]}
+    for ln in res.stdout.splitlines():
+        if ln.startswith("{"):
+            return json.loads(ln)["edm_dp_train"]
+    return {"error": "no result line"}
+
+
 # ------------------------------------------------------------------------------------ main
 KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd": 2 * NEL * 4, "ln_bwd": 3 * NEL * 4,
                 "sinusoidal": B * EMB * 4}
@@ -627,6 +654,14 @@ def main():
         torch.cuda.empty_cache()
         step = None
         line["sharded_adam_ema"] = sharded_adam_ema(lib, world, rank)
+        # EDM UNet training, images/s: weak scaling (256 per GPU) and strong scaling (256 in total)
+        if world > 1:
+            torch.distributed.barrier()
+        dp = {"weak_256_per_gpu": edm_dp_train(world, rank, local, 256)}
+        if world > 1:
+            torch.distributed.barrier()
+            dp["strong_256_global"] = edm_dp_train(world, rank, local, 256 // world)
+        line["edm_dp_train"] = dp
     if rank == 0:
         if not args.no_cpu and (world == 1 or args.impl == "reference"):
             line["cpu_baseline"] = cpu_baseline()
