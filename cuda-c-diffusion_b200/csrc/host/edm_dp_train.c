@@ -16,8 +16,8 @@
  *
  * Usage: edm_dp_train [--steps K] [--warmup W] [--batch B_local] [--check] [--fp32] [--graph]
  *                     [--id-file PATH] [--seed S] [--log-every N]
- *   --graph: forward + backward + gradient all-reduce are captured into one CUDA graph on the
- *   last warm-up step and replayed afterwards (uploads, noise and the update stay outside).
+ *   --graph: forward + backward are captured into one CUDA graph on the last warm-up step and
+ *   replayed afterwards (uploads, noise, the gradient all-reduce and the update stay outside).
  *   RANK / WORLD_SIZE / LOCAL_RANK come from the environment (torchrun sets them).
  *   --check (single rank): runs the reference's own edm_loss_step + optimizer_step + ema_update
  *   and this file's step from identical state and prints the largest relative differences.
@@ -381,6 +381,15 @@ static void exchange_id(ncclUniqueId* id, int rank, const char* path)
     exit(1);
 }
 
+static int g_verbose = 0;
+#define TRACE(...)                                  \
+    do {                                            \
+        if (g_verbose) {                            \
+            fprintf(stderr, __VA_ARGS__);           \
+            fflush(stderr);                         \
+        }                                           \
+    } while (0)
+
 static int env_int(const char* name, int dflt)
 {
     const char* v = getenv(name);
@@ -401,6 +410,7 @@ int main(int argc, char** argv)
         else if (!strcmp(argv[i], "--log-every") && i + 1 < argc) log_every = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--check")) check = 1;
         else if (!strcmp(argv[i], "--graph")) use_graph = 1;
+        else if (!strcmp(argv[i], "--verbose")) g_verbose = 1;
         else if (!strcmp(argv[i], "--fp32")) tf32 = 0;
         else {
             fprintf(stderr, "unknown argument %s\n", argv[i]);
@@ -428,7 +438,9 @@ int main(int argc, char** argv)
     if (world > 1) {
         ncclUniqueId id;
         exchange_id(&id, rank, id_file);
+        TRACE("rank %d: have the NCCL id\n", rank);
         NCCL_OK(ncclCommInitRank(&comm, world, id, rank));
+        TRACE("rank %d: communicator ready\n", rank);
     }
 
     /* identical initial weights on every rank (same seed); noise and batches differ per rank */
@@ -438,6 +450,7 @@ int main(int argc, char** argv)
     ParamList params;
     param_list_init(&params);
     dp_model_parameters(m, &params);
+    TRACE("rank %d: model built\n", rank);
     const float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, decay = 0.999f;
     Optimizer* opt = optimizer_adam(&params, lr, b1, b2, eps);
     EMA* ema = ema_create(&params, decay);
@@ -490,13 +503,6 @@ int main(int argc, char** argv)
             if (capture)
                 NN_CUDA_CHECK(cudaStreamBeginCapture(ctx.stream, cudaStreamCaptureModeThreadLocal));
             dp_forward_backward(m, &ctx);
-            if (comm) {
-                NCCL_OK(ncclGroupStart());
-                for (int i = 0; i < params.count; ++i)
-                    NCCL_OK(ncclAllReduce(params.items[i].grad, params.items[i].grad, (size_t)params.items[i].size,
-                        ncclFloat, ncclSum, comm, ctx.stream));
-                NCCL_OK(ncclGroupEnd());
-            }
             if (capture) {
                 cudaGraph_t graph = NULL;
                 NN_CUDA_CHECK(cudaStreamEndCapture(ctx.stream, &graph));
@@ -506,7 +512,18 @@ int main(int argc, char** argv)
                 NN_CUDA_CHECK(cudaGraphLaunch(graph_exec, ctx.stream));
             }
         }
+        /* The gradient exchange stays outside the graph: with the grouped all-reduce captured,
+           two ranks stopped making progress after the capture step (NCCL 2.27.3), so it is
+           issued as one ordinary grouped launch per step. */
+        if (comm) {
+            NCCL_OK(ncclGroupStart());
+            for (int i = 0; i < params.count; ++i)
+                NCCL_OK(ncclAllReduce(params.items[i].grad, params.items[i].grad, (size_t)params.items[i].size,
+                    ncclFloat, ncclSum, comm, ctx.stream));
+            NCCL_OK(ncclGroupEnd());
+        }
         optimizer_ema_step_fused(opt, ema, &params, cur_lr, b1, b2, eps, decay, 1.0f / (float)world, &ctx);
+        TRACE("rank %d: step %d enqueued\n", rank, step);
         const int logging = step == 1 || step == warmup + steps || (log_every > 0 && step % log_every == 0);
         if (logging && (step <= warmup || step == warmup + steps)) {
             /* the last step's read-back is inside the timed region on purpose: it is the
@@ -520,6 +537,7 @@ int main(int argc, char** argv)
     }
     NN_CUDA_CHECK(cudaEventRecord(ev1, ctx.stream));
     NN_CUDA_CHECK(cudaStreamSynchronize(ctx.stream));
+    TRACE("rank %d: all steps finished\n", rank);
     launches_timed = b200_launch_count() - launches_timed;
     float ms = 0.0f;
     NN_CUDA_CHECK(cudaEventElapsedTime(&ms, ev0, ev1));

@@ -32,3 +32,46 @@ def test_c_host_modules_of_fused_entry_points():
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "0 failure(s)" in res.stdout
     assert res.stdout.count("PASS") == 25 and "FAIL" not in res.stdout
+
+
+def test_edm_dp_step_matches_reference_step():
+    """csrc/host/edm_dp_train.c --check: the batched data-parallel step against the reference's own
+    edm_loss_step + optimizer_step + ema_update from identical state (fp32 GEMMs, two steps)."""
+    res = subprocess.run([str(ROOT / "oracle" / "_ref" / "edm_dp_train"), "--check"], capture_output=True, text=True,
+                         timeout=600) if (ROOT / "oracle" / "_ref" / "edm_dp_train").exists() else None
+    if res is None:
+        pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
+    print(res.stdout[-3000:])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "0 failure(s)" in res.stdout and res.stdout.count("PASS") == 9
+
+
+def test_edm_dp_two_ranks_stay_in_sync(tmp_path):
+    """Two trainer processes, one per GPU, NCCL gradient all-reduce: replicas must hold identical parameters
+    after the run, eager and with the CUDA graph."""
+    import json
+    import os
+    import torch
+    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+    if not exe.exists():
+        pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    for extra in ([], ["--graph"]):
+        id_file = tmp_path / ("id" + "_".join(extra))
+        procs = []
+        for r in range(2):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), NCCL_NVLS_ENABLE="0")
+            procs.append(subprocess.Popen([str(exe), "--batch", "16", "--steps", "4", "--warmup", "3", "--id-file",
+                                           str(id_file)] + extra, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                                          text=True))
+        try:
+            outs = [p.communicate(timeout=120) for p in procs]
+        except subprocess.TimeoutExpired:
+            for p in procs:
+                p.kill()
+            pytest.fail(f"trainer ranks did not finish within 120 s ({extra})")
+        assert all(p.returncode == 0 for p in procs), outs
+        line = next(ln for ln in outs[0][0].splitlines() if ln.startswith("{"))
+        got = json.loads(line)["edm_dp_train"]
+        assert got["replicas_in_sync"] is True and got["n_gpus"] == 2 and got["b200_device_error"] == 0
