@@ -246,6 +246,109 @@ __device__ __forceinline__ float act_slope(float z)
     }
 }
 
+// --- packed fp32 pairs -------------------------------------------------------
+// sm_100 executes add/mul/fma on two fp32 values held in one 64-bit register
+// (f32x2) as a single instruction.  The GroupNorm strip kernels are limited by
+// instruction issue as much as by HBM, so their per-element arithmetic runs on
+// pairs.  Each lane is an ordinary IEEE fp32 operation: results are bit-identical
+// to the scalar forms.
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pk(float lo, float hi)
+{
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pk1(float v) { return pk(v, v); }
+__device__ __forceinline__ void unpk(f32x2 v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 pk_fma(f32x2 a, f32x2 b, f32x2 c)
+{
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 pk_mul(f32x2 a, f32x2 b)
+{
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 pk_add(f32x2 a, f32x2 b)
+{
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// rational_sigmoid on a pair.  Differences from the scalar form, both below 1 ulp of the
+// result: the numerator carries the final factor 1/2 (exact power-of-two scaling) so that
+// t/2 + 1/2 is ONE fused multiply-add of numerator and reciprocal, and the clamp of t to
+// [-1, 1] becomes the saturation of that result to [0, 1] (same value for every finite t).
+__device__ __forceinline__ void rational_sigmoid_x2(f32x2 x, float& s0, float& s1)
+{
+    const f32x2 x2 = pk_mul(x, x);
+    f32x2 n = pk_fma(x2, pk1(0.001953125f), pk1(2.953125f));
+    n = pk_fma(n, x2, pk1(541.40625f));
+    n = pk_fma(n, x2, pk1(16891.875f));
+    n = pk_mul(n, x);
+    f32x2 d = pk_fma(x2, pk1(0.21875f), pk1(98.4375f));
+    d = pk_fma(d, x2, pk1(7796.25f));
+    d = pk_fma(d, x2, pk1(67567.5f));
+    float n0, n1, d0, d1, r0, r1;
+    unpk(n, n0, n1);
+    unpk(d, d0, d1);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
+    asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(s0) : "f"(n0), "f"(r0));
+    asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(s1) : "f"(n1), "f"(r1));
+}
+
+// act_value / act_slope on a pair of pre-activations (SiLU family on packed arithmetic,
+// everything else through the scalar forms)
+template <int ACT>
+__device__ __forceinline__ f32x2 act_value_x2(f32x2 z)
+{
+    if constexpr (ACT == ACT_SILU || ACT == ACT_MP_SILU) {
+        float s0, s1;
+        rational_sigmoid_x2(z, s0, s1);
+        f32x2 o = pk_mul(z, pk(s0, s1));
+        if constexpr (ACT == ACT_MP_SILU)
+            o = pk_mul(o, pk1(B200_MP_SILU_SCALE));
+        return o;
+    } else if constexpr (ACT == ACT_IDENTITY) {
+        return z;
+    } else {
+        float z0, z1;
+        unpk(z, z0, z1);
+        return pk(act_value<ACT>(z0), act_value<ACT>(z1));
+    }
+}
+
+template <int ACT>
+__device__ __forceinline__ f32x2 act_slope_x2(f32x2 z)
+{
+    if constexpr (ACT == ACT_SILU || ACT == ACT_MP_SILU) {
+        float s0, s1;
+        rational_sigmoid_x2(z, s0, s1);
+        const f32x2 s = pk(s0, s1);
+        const f32x2 one = pk1(1.0f);
+        // s * (1 + z * (1 - s))
+        const f32x2 oms = pk_fma(s, pk1(-1.0f), one);
+        f32x2 r = pk_mul(s, pk_fma(z, oms, one));
+        if constexpr (ACT == ACT_MP_SILU)
+            r = pk_mul(r, pk1(B200_MP_SILU_SCALE));
+        return r;
+    } else {
+        float z0, z1;
+        unpk(z, z0, z1);
+        return pk(act_slope<ACT>(z0), act_slope<ACT>(z1));
+    }
+}
+
 // --- mbarrier / bulk tensor copy (TMA) primitives ----------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p)
 {

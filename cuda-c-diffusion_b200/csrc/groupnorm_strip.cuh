@@ -359,12 +359,22 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
         if (item + (int)gridDim.x < nitems)
             strip_prefetch<NT, VPT, 1>(stage, g, item + gridDim.x, q, rl, x, nullptr);
 
-        float4 s1 = make_float4(0.f, 0.f, 0.f, 0.f), s2 = s1;
+        float4 s1, s2;
+        {
+            const f32x2 nk01 = pk(-K.x, -K.y), nk23 = pk(-K.z, -K.w);
+            f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            const float d0 = v[j].x - K.x, d1 = v[j].y - K.y, d2 = v[j].z - K.z, d3 = v[j].w - K.w;
-            s1.x += d0; s1.y += d1; s1.z += d2; s1.w += d3;
-            s2.x = fmaf(d0, d0, s2.x); s2.y = fmaf(d1, d1, s2.y); s2.z = fmaf(d2, d2, s2.z); s2.w = fmaf(d3, d3, s2.w);
+            for (int j = 0; j < VPT; ++j) {
+                const f32x2 d01 = pk_add(pk(v[j].x, v[j].y), nk01), d23 = pk_add(pk(v[j].z, v[j].w), nk23);
+                a1 = pk_add(a1, d01);
+                b1 = pk_add(b1, d23);
+                a2 = pk_fma(d01, d01, a2);
+                b2 = pk_fma(d23, d23, b2);
+            }
+            unpk(a1, s1.x, s1.y);
+            unpk(b1, s1.z, s1.w);
+            unpk(a2, s2.x, s2.y);
+            unpk(b2, s2.z, s2.w);
         }
         strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, s1, s2);
         if (t < g.Gt) {
@@ -396,15 +406,14 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
         sc.y = ga.y * gstat[g.Gt + g1]; sh.y = be.y - gstat[g1] * sc.y;
         sc.z = ga.z * gstat[g.Gt + g2]; sh.z = be.z - gstat[g2] * sc.z;
         sc.w = ga.w * gstat[g.Gt + g3]; sh.w = be.w - gstat[g3] * sc.w;
+        const f32x2 sc01 = pk(sc.x, sc.y), sc23 = pk(sc.z, sc.w), sh01 = pk(sh.x, sh.y), sh23 = pk(sh.z, sh.w);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int r = rl + j * g.RSTEP;
             if (FULL || r < g.HW) {
                 float4 o;
-                o.x = act_value<ACT>(fmaf(v[j].x, sc.x, sh.x));
-                o.y = act_value<ACT>(fmaf(v[j].y, sc.y, sh.y));
-                o.z = act_value<ACT>(fmaf(v[j].z, sc.z, sh.z));
-                o.w = act_value<ACT>(fmaf(v[j].w, sc.w, sh.w));
+                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].x, v[j].y), sc01, sh01)), o.x, o.y);
+                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].z, v[j].w), sc23, sh23)), o.z, o.w);
                 __stcs(reinterpret_cast<float4*>(y + base + (size_t)r * g.C), o);
             }
         }
@@ -465,24 +474,34 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
         if (item + (int)gridDim.x < nitems)
             strip_prefetch<NT, VPT, 2>(stage, g, item + gridDim.x, q, rl, x, dy);
 
-        float4 sA = make_float4(0.f, 0.f, 0.f, 0.f), sB = sA;
+        // xv becomes xhat, dv becomes dy * act'(z), both kept as packed pairs for the second phase
+        const f32x2 rs01 = pk(rs4.x, rs4.y), rs23 = pk(rs4.z, rs4.w), nm01 = pk(nm4.x, nm4.y), nm23 = pk(nm4.z, nm4.w);
+        const f32x2 ga01 = pk(ga.x, ga.y), ga23 = pk(ga.z, ga.w), be01 = pk(be.x, be.y), be23 = pk(be.z, be.w);
+        f32x2 xa[VPT], xb[VPT], da[VPT], db[VPT];
+        float4 sA, sB;
+        {
+            f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            if (rl + j * g.RSTEP < g.HW) {
-                xv[j].x = fmaf(xv[j].x, rs4.x, nm4.x);
-                xv[j].y = fmaf(xv[j].y, rs4.y, nm4.y);
-                xv[j].z = fmaf(xv[j].z, rs4.z, nm4.z);
-                xv[j].w = fmaf(xv[j].w, rs4.w, nm4.w);
+            for (int j = 0; j < VPT; ++j) {
+                xa[j] = pk_fma(pk(xv[j].x, xv[j].y), rs01, nm01);
+                xb[j] = pk_fma(pk(xv[j].z, xv[j].w), rs23, nm23);
+                da[j] = pk(dv[j].x, dv[j].y);
+                db[j] = pk(dv[j].z, dv[j].w);
                 if (ACT != ACT_IDENTITY) {
-                    dv[j].x *= act_slope<ACT>(fmaf(ga.x, xv[j].x, be.x));
-                    dv[j].y *= act_slope<ACT>(fmaf(ga.y, xv[j].y, be.y));
-                    dv[j].z *= act_slope<ACT>(fmaf(ga.z, xv[j].z, be.z));
-                    dv[j].w *= act_slope<ACT>(fmaf(ga.w, xv[j].w, be.w));
+                    da[j] = pk_mul(da[j], act_slope_x2<ACT>(pk_fma(ga01, xa[j], be01)));
+                    db[j] = pk_mul(db[j], act_slope_x2<ACT>(pk_fma(ga23, xb[j], be23)));
                 }
-                sA.x += dv[j].x; sA.y += dv[j].y; sA.z += dv[j].z; sA.w += dv[j].w;
-                sB.x = fmaf(dv[j].x, xv[j].x, sB.x); sB.y = fmaf(dv[j].y, xv[j].y, sB.y);
-                sB.z = fmaf(dv[j].z, xv[j].z, sB.z); sB.w = fmaf(dv[j].w, xv[j].w, sB.w);
+                if (rl + j * g.RSTEP < g.HW) {
+                    a1 = pk_add(a1, da[j]);
+                    b1 = pk_add(b1, db[j]);
+                    a2 = pk_fma(da[j], xa[j], a2);
+                    b2 = pk_fma(db[j], xb[j], b2);
+                }
             }
+            unpk(a1, sA.x, sA.y);
+            unpk(b1, sA.z, sA.w);
+            unpk(a2, sB.x, sB.y);
+            unpk(b2, sB.z, sB.w);
         }
         strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, sA, sB);
         if (t < g.Gt) {
@@ -508,15 +527,15 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
         mg.y = gstat[gl1]; mgx.y = gstat[g.Gt + gl1];
         mg.z = gstat[gl2]; mgx.z = gstat[g.Gt + gl2];
         mg.w = gstat[gl3]; mgx.w = gstat[g.Gt + gl3];
+        // dx = rstd * (g*gamma - mg - xhat*mgx), as in the reference (kernels.cu:692)
+        const f32x2 nmg01 = pk(-mg.x, -mg.y), nmg23 = pk(-mg.z, -mg.w), nmx01 = pk(-mgx.x, -mgx.y), nmx23 = pk(-mgx.z, -mgx.w);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int r = rl + j * g.RSTEP;
             if (r < g.HW) {
                 float4 o;
-                o.x = rs4.x * (fmaf(dv[j].x, ga.x, -mg.x) - xv[j].x * mgx.x);
-                o.y = rs4.y * (fmaf(dv[j].y, ga.y, -mg.y) - xv[j].y * mgx.y);
-                o.z = rs4.z * (fmaf(dv[j].z, ga.z, -mg.z) - xv[j].z * mgx.z);
-                o.w = rs4.w * (fmaf(dv[j].w, ga.w, -mg.w) - xv[j].w * mgx.w);
+                unpk(pk_mul(rs01, pk_fma(xa[j], nmx01, pk_fma(da[j], ga01, nmg01))), o.x, o.y);
+                unpk(pk_mul(rs23, pk_fma(xb[j], nmx23, pk_fma(db[j], ga23, nmg23))), o.z, o.w);
                 __stcs(reinterpret_cast<float4*>(dx + base + (size_t)r * g.C), o);
             }
         }
