@@ -504,16 +504,17 @@ def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
                 "steps_timed": nst, "how": "wall-clock difference of two runs of the unmodified reference trainer"}
 
 
-def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True):
-    """Data-parallel EDM UNet training (oracle/_ref/edm_dp_train: the reference's UNet and host modules, this
-    library's kernels, NCCL gradient all-reduce).  Every rank of this benchmark starts one trainer process on
-    its own GPU; the trainers find each other through a file named after MASTER_PORT.  Rank 0 returns the
-    trainer's JSON (device-timed, max over ranks), the other ranks None."""
-    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True, fastconv=True):
+    """Data-parallel EDM UNet training (oracle/_ref/edm_dp_train[_fastconv]: the reference's UNet and host
+    modules, this library's kernels, NCCL gradient all-reduce; `fastconv` links csrc/host/b200_conv2d.c in place of
+    the reference's conv2d.c).  Every rank of this benchmark starts one trainer process on its own GPU; the
+    trainers find each other through a file named after MASTER_PORT.  Rank 0 returns the trainer's JSON
+    (device-timed, max over ranks), the other ranks None."""
+    exe = ROOT / "oracle" / "_ref" / ("edm_dp_train_fastconv" if fastconv else "edm_dp_train")
     if not exe.exists():
         return None
     env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local_rank))
-    id_file = f"/tmp/edm_dp_train_{os.environ.get('MASTER_PORT', '0')}_{batch_per_gpu}.ncclid"
+    id_file = f"/tmp/edm_dp_train_{os.environ.get('MASTER_PORT', '0')}_{batch_per_gpu}_{int(fastconv)}.ncclid"
     cmd = [str(exe), "--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup), "--id-file", id_file]
     if graph:
         cmd.append("--graph")
@@ -527,7 +528,9 @@ def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, gra
         return {"error": (res.stderr or res.stdout)[-300:]}
     for ln in res.stdout.splitlines():
         if ln.startswith("{"):
-            return json.loads(ln)["edm_dp_train"]
+            got = json.loads(ln)["edm_dp_train"]
+            got["conv2d_host_module"] = "csrc/host/b200_conv2d.c" if fastconv else "reference src/conv2d.c"
+            return got
     return {"error": "no result line"}
 
 
@@ -661,6 +664,8 @@ def main():
         if world > 1:
             torch.distributed.barrier()
             dp["strong_256_global"] = edm_dp_train(world, rank, local, 256 // world)
+        else:
+            dp["weak_256_per_gpu_reference_conv2d"] = edm_dp_train(world, rank, local, 256, fastconv=False)
         line["edm_dp_train"] = dp
     if rank == 0:
         if not args.no_cpu and (world == 1 or args.impl == "reference"):

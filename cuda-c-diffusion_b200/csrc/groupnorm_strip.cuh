@@ -322,6 +322,15 @@ __device__ __forceinline__ void strip_prefetch(float4* stage, const StripGeom& g
 
 // grid = min(items, resident CTAs), block = NT; dynamic smem = stage | red | chan | gstat
 // FULL: HW == RSTEP * VPT, i.e. every register slot holds a real row and no row test is needed.
+//
+// Measured dead ends, kept out on purpose (same-GPU A/B, [256,32,32,256], SiLU):
+//  - fetching the next strip's shift K one strip ahead, or serving the group-statistics threads
+//    from shared memory instead of global loads: the extra live registers spill at the 64-register
+//    limit, forward 4-6 % slower;
+//  - 32-bit float4 indexing with no division in the strip loop and a FULL backward: a quarter
+//    fewer instructions, forward unchanged, backward 4 % slower.  With the packed arithmetic these
+//    kernels are no longer bound by instruction issue but by the latency of one strip's dependent
+//    phases (16-32 resident warps per SM is all the register-resident strip allows).
 template <int NT, int VPT, int ACT, int MB, bool FULL>
 __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
     float* __restrict__ mu, float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,

@@ -15,7 +15,8 @@
  *   - Adam and the EMA update are one multi-tensor launch (optimizer_ema_step_fused).
  *
  * Usage: edm_dp_train [--steps K] [--warmup W] [--batch B_local] [--check] [--fp32] [--graph]
- *                     [--id-file PATH] [--seed S] [--log-every N]
+ *                     [--id-file PATH] [--seed S] [--log-every N] [--dump FILE]
+ *   --dump FILE: rank 0 writes the last loss and all parameters (raw float32) after the run.
  *   --graph: forward + backward are captured into one CUDA graph on the last warm-up step and
  *   replayed afterwards (uploads, noise, the gradient all-reduce and the update stay outside).
  *   RANK / WORLD_SIZE / LOCAL_RANK come from the environment (torchrun sets them).
@@ -401,6 +402,7 @@ int main(int argc, char** argv)
     int steps = 20, warmup = 5, batch = 256, check = 0, tf32 = 1, log_every = 0, use_graph = 0;
     unsigned seed = 410293;
     const char* id_file = "/tmp/edm_dp_train.ncclid";
+    const char* dump_path = NULL;
     for (int i = 1; i < argc; ++i) {
         if (!strcmp(argv[i], "--steps") && i + 1 < argc) steps = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--warmup") && i + 1 < argc) warmup = atoi(argv[++i]);
@@ -408,6 +410,7 @@ int main(int argc, char** argv)
         else if (!strcmp(argv[i], "--seed") && i + 1 < argc) seed = (unsigned)atoi(argv[++i]);
         else if (!strcmp(argv[i], "--id-file") && i + 1 < argc) id_file = argv[++i];
         else if (!strcmp(argv[i], "--log-every") && i + 1 < argc) log_every = atoi(argv[++i]);
+        else if (!strcmp(argv[i], "--dump") && i + 1 < argc) dump_path = argv[++i];
         else if (!strcmp(argv[i], "--check")) check = 1;
         else if (!strcmp(argv[i], "--graph")) use_graph = 1;
         else if (!strcmp(argv[i], "--verbose")) g_verbose = 1;
@@ -567,6 +570,21 @@ int main(int argc, char** argv)
             params.count, tf32, (double)launches_timed / steps, graph_nodes, first_loss, last_loss, in_sync ? "true" : "false",
             b200_device_error_status());
 
+    if (dump_path && rank == 0) { /* last loss, then every parameter tensor, as raw float32 */
+        FILE* f = fopen(dump_path, "wb");
+        if (!f) {
+            fprintf(stderr, "cannot write %s\n", dump_path);
+            return 1;
+        }
+        fwrite(&last_loss, sizeof(float), 1, f);
+        for (int i = 0; i < params.count; ++i) {
+            float* h = (float*)malloc((size_t)params.items[i].size * sizeof(float));
+            NN_CUDA_CHECK(cudaMemcpy(h, params.items[i].param, (size_t)params.items[i].size * sizeof(float), cudaMemcpyDeviceToHost));
+            fwrite(h, sizeof(float), (size_t)params.items[i].size, f);
+            free(h);
+        }
+        fclose(f);
+    }
     if (comm)
         ncclCommDestroy(comm);
     if (rank == 0 && world > 1)

@@ -75,3 +75,32 @@ def test_edm_dp_two_ranks_stay_in_sync(tmp_path):
         line = next(ln for ln in outs[0][0].splitlines() if ln.startswith("{"))
         got = json.loads(line)["edm_dp_train"]
         assert got["replicas_in_sync"] is True and got["n_gpus"] == 2 and got["b200_device_error"] == 0
+
+
+def test_reference_gradcheck_passes_with_replaced_conv2d_host_module():
+    """The reference's gradcheck with its conv2d.c replaced at link time by csrc/host/b200_conv2d.c."""
+    res = _run(ROOT / "oracle" / "_ref" / "gradcheck_b200_fastconv")
+    print(res.stdout[-3000:])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "ALL GRADIENTS OK" in res.stdout
+    assert res.stdout.count("[PASS]") == 15
+
+
+def test_replaced_conv2d_trains_to_the_same_parameters(tmp_path):
+    """Five fp32 training steps with the reference's conv2d host module and with the replacement
+    (gain as GEMM alpha, column buffer reused, 1x1 as plain GEMM) from the same seed: same loss and parameters."""
+    import numpy as np
+    outs = {}
+    for name in ("edm_dp_train", "edm_dp_train_fastconv"):
+        exe = ROOT / "oracle" / "_ref" / name
+        if not exe.exists():
+            pytest.skip(f"{name} not built (needs the reference sources at build time)")
+        dump = tmp_path / (name + ".bin")
+        res = subprocess.run([str(exe), "--fp32", "--steps", "3", "--warmup", "2", "--batch", "16", "--dump", str(dump)],
+                             capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        outs[name] = np.fromfile(dump, dtype=np.float32)
+    a, b = outs["edm_dp_train"], outs["edm_dp_train_fastconv"]
+    assert a.size == b.size and a.size > 1_000_000
+    assert abs(a[0] - b[0]) <= 1e-5 * abs(a[0])                       # loss of the last step
+    assert np.abs(a[1:] - b[1:]).max() <= 1e-5 * np.abs(a[1:]).max()  # every parameter
