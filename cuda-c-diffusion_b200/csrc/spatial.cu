@@ -50,6 +50,36 @@ __global__ void __launch_bounds__(256) im2col_kernel(float* __restrict__ col, co
     }
 }
 
+// float4 fast path: one thread per (output pixel, channel pack).  The coordinates are decoded once
+// (32-bit arithmetic) and the K*K taps are then walked with all loads in flight, so the index
+// arithmetic is paid once per K*K stores instead of once per store.  KT = K at compile time (0: runtime).
+template <int KT>
+__global__ void __launch_bounds__(256) im2col_taps_kernel(float4* __restrict__ col, const float4* __restrict__ im,
+    int H, int W, int Cv, int K, int stride, int pad, int Ho, int Wo, unsigned total)
+{
+    const int Kk = KT ? KT : K;
+    const unsigned row4 = (unsigned)(Kk * Kk) * (unsigned)Cv;  // float4 per col row
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned p = i / (unsigned)Cv, cv = i - p * (unsigned)Cv;
+        const unsigned ow = p % (unsigned)Wo, t2 = p / (unsigned)Wo;
+        const unsigned oh = t2 % (unsigned)Ho, b = t2 / (unsigned)Ho;
+        const int ih0 = (int)oh * stride - pad, iw0 = (int)ow * stride - pad;
+        const float4* src = im + (size_t)b * H * W * Cv + cv;
+        float4* dst = col + (size_t)p * row4 + cv;
+#pragma unroll
+        for (int kh = 0; kh < Kk; ++kh) {
+#pragma unroll
+            for (int kw = 0; kw < Kk; ++kw) {
+                const int ih = ih0 + kh, iw = iw0 + kw;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+                    v = __ldg(src + (size_t)(ih * W + iw) * Cv);
+                __stcs(dst + (kh * Kk + kw) * Cv, v);
+            }
+        }
+    }
+}
+
 // grad_im[b,ih,iw,c] += sum over the (kh,kw) taps whose output pixel exists
 template <int V>
 __global__ void __launch_bounds__(256) col2im_gather_kernel(float* __restrict__ grad_im,
@@ -332,7 +362,17 @@ void launch_im2col(float* col, const float* im, int batch, int H, int W, int C, 
     const long n = (long)batch * H_out * W_out * K * K * C;
     if (n == 0)
         return;
-    if (C % 4 == 0 && aligned16(col) && aligned16(im))
+    const long units = (long)batch * H_out * W_out * (C / 4);  // (pixel, channel pack) pairs
+    if (C % 4 == 0 && aligned16(col) && aligned16(im) && units < 4294967296L && !tune_get("im2col_flat", 0)) {
+        const float4* im4 = reinterpret_cast<const float4*>(im);
+        float4* col4 = reinterpret_cast<float4*>(col);
+        if (K == 3)
+            im2col_taps_kernel<3><<<flat_grid(units), 256, 0, s>>>(col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
+                (unsigned)units);
+        else
+            im2col_taps_kernel<0><<<flat_grid(units), 256, 0, s>>>(col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
+                (unsigned)units);
+    } else if (C % 4 == 0 && aligned16(col) && aligned16(im))
         im2col_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(col, im, H, W, C, K, stride, pad, H_out, W_out, n / 4);
     else
         im2col_kernel<1><<<flat_grid(n), 256, 0, s>>>(col, im, H, W, C, K, stride, pad, H_out, W_out, n);

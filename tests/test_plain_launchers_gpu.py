@@ -46,8 +46,8 @@ rng = np.random.default_rng(1234)
 f = lambda *s: rng.standard_normal(s, dtype=np.float32)
 
 
-@pytest.mark.parametrize("C", [4, 3])
-@pytest.mark.parametrize("K,stride,pad", [(3, 1, 1), (1, 1, 0), (3, 2, 1)])
+@pytest.mark.parametrize("C", [4, 3, 16])
+@pytest.mark.parametrize("K,stride,pad", [(3, 1, 1), (1, 1, 0), (3, 2, 1), (2, 1, 0), (5, 1, 2)])
 def test_im2col_col2im(lib, orc, C, K, stride, pad):
     import torch
     B, H, W = 2, 6, 5
