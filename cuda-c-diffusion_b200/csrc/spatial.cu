@@ -127,6 +127,38 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(float* __restrict__ 
     }
 }
 
+// float4, stride-1 fast path of the gather: one thread per (input pixel, channel pack), coordinates
+// decoded once in 32-bit arithmetic, the K*K candidate taps unrolled so that their loads overlap.
+template <int KT>
+__global__ void __launch_bounds__(256) col2im_taps_kernel(float4* __restrict__ grad_im,
+    const float4* __restrict__ grad_col, int H, int W, int Cv, int K, int pad, int Ho, int Wo, unsigned total)
+{
+    const int Kk = KT ? KT : K;
+    const unsigned row4 = (unsigned)(Kk * Kk) * (unsigned)Cv;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned pix = i / (unsigned)Cv, cv = i - pix * (unsigned)Cv;
+        const unsigned iw = pix % (unsigned)W, t2 = pix / (unsigned)W;
+        const unsigned ih = t2 % (unsigned)H, b = t2 / (unsigned)H;
+        const float4* src = grad_col + (size_t)b * Ho * Wo * row4 + cv;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int kh = 0; kh < Kk; ++kh) {
+            const int oh = (int)ih + pad - kh;
+#pragma unroll
+            for (int kw = 0; kw < Kk; ++kw) {
+                const int ow = (int)iw + pad - kw;
+                if (oh >= 0 && oh < Ho && ow >= 0 && ow < Wo) {
+                    const float4 g = __ldcs(src + (size_t)(oh * Wo + ow) * row4 + (kh * Kk + kw) * Cv);
+                    acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+                }
+            }
+        }
+        float4 old = grad_im[i];
+        old.x += acc.x; old.y += acc.y; old.z += acc.z; old.w += acc.w;
+        grad_im[i] = old;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // 2x average pool / nearest upsample and their backwards
 // MODE 0: avg pool fwd (out [B,H/2,W/2,C])      MODE 1: avg pool bwd (writes the 4 covered inputs)
@@ -388,7 +420,17 @@ void launch_col2im(float* grad_im, const float* grad_col, int batch, int H, int 
     const long n = (long)batch * H * W * C;
     if (n == 0)
         return;
-    if (C % 4 == 0 && aligned16(grad_im) && aligned16(grad_col))
+    if (C % 4 == 0 && stride == 1 && aligned16(grad_im) && aligned16(grad_col) && n / 4 < 4294967296L
+        && (long)batch * H_out * W_out * K * K * (C / 4) < 4294967296L && !tune_get("col2im_flat", 0)) {
+        float4* gi4 = reinterpret_cast<float4*>(grad_im);
+        const float4* gc4 = reinterpret_cast<const float4*>(grad_col);
+        if (K == 3)
+            col2im_taps_kernel<3><<<flat_grid(n / 4), 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out,
+                (unsigned)(n / 4));
+        else
+            col2im_taps_kernel<0><<<flat_grid(n / 4), 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out,
+                (unsigned)(n / 4));
+    } else if (C % 4 == 0 && aligned16(grad_im) && aligned16(grad_col))
         col2im_gather_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(grad_im, grad_col, H, W, C, K, stride, pad, H_out,
             W_out, n / 4);
     else
