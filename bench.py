@@ -557,7 +557,7 @@ def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, gra
     if graph:
         cmd.append("--graph")
     try:
-        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=90)
     except subprocess.TimeoutExpired:
         return {"error": "timeout"} if rank == 0 else None
     if rank != 0:
