@@ -68,6 +68,10 @@ SIGNATURES = {
     "launch_adam_ema_step": "pppppffffffffqs",
     "launch_adam_ema_step_multi": "hiffffffffs",
     "launch_weight_normalize_multi": "hifs",
+    "launch_weight_normalize_backward_multi": "his",
+    "b200_wn_batch_mode": "i",
+    "b200_wn_forward_all": "s",
+    "b200_wn_backward_flush": "s",
     "launch_axpby_rows": "pppppiis",
     "launch_layernorm_backward_noalloc": "ppppppppiis",
     # management
@@ -87,6 +91,8 @@ SIGNATURES = {
 RETURNS = {
     "launch_layernorm_backward_noalloc": ctypes.c_int,
     "b200_error_count": ctypes.c_int,
+    "b200_wn_forward_all": ctypes.c_int,
+    "b200_wn_backward_flush": ctypes.c_int,
     "b200_last_error": ctypes.c_int,
     "b200_device_error_status": ctypes.c_int,
     "b200_launch_count": ctypes.c_longlong,
@@ -117,6 +123,12 @@ class ParamUpdate(ctypes.Structure):
 class WeightDesc(ctypes.Structure):
     """B200WeightDesc of include/b200_layer_kernels.h."""
     _fields_ = [("W", ctypes.c_void_p), ("rows_in", ctypes.c_int), ("cols_out", ctypes.c_int)]
+
+
+class WeightGradDesc(ctypes.Structure):
+    """B200WeightGradDesc of include/b200_layer_kernels.h."""
+    _fields_ = [("gW", ctypes.c_void_p), ("Wn", ctypes.c_void_p), ("gain", ctypes.c_void_p), ("g_gain", ctypes.c_void_p),
+                ("rows_in", ctypes.c_int), ("cols_out", ctypes.c_int)]
 
 
 def bind(lib: ctypes.CDLL, signatures=None) -> ctypes.CDLL:

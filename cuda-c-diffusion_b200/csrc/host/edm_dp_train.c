@@ -17,6 +17,7 @@
  * Usage: edm_dp_train [--steps K] [--warmup W] [--batch B_local] [--check] [--fp32] [--graph]
  *                     [--id-file PATH] [--seed S] [--log-every N] [--dump FILE]
  *   --dump FILE: rank 0 writes the last loss and all parameters (raw float32) after the run.
+ *   --no-wn-batch: keep one weight-normalisation launch per weight (default: one launch for all).
  *   --graph: forward + backward are captured into one CUDA graph on the last warm-up step and
  *   replayed afterwards (uploads, noise, the gradient all-reduce and the update stay outside).
  *   RANK / WORLD_SIZE / LOCAL_RANK come from the environment (torchrun sets them).
@@ -399,7 +400,7 @@ static int env_int(const char* name, int dflt)
 
 int main(int argc, char** argv)
 {
-    int steps = 20, warmup = 5, batch = 256, check = 0, tf32 = 1, log_every = 0, use_graph = 0;
+    int steps = 20, warmup = 5, batch = 256, check = 0, tf32 = 1, log_every = 0, use_graph = 0, batch_wn = 1;
     unsigned seed = 410293;
     const char* id_file = "/tmp/edm_dp_train.ncclid";
     const char* dump_path = NULL;
@@ -413,6 +414,7 @@ int main(int argc, char** argv)
         else if (!strcmp(argv[i], "--dump") && i + 1 < argc) dump_path = argv[++i];
         else if (!strcmp(argv[i], "--check")) check = 1;
         else if (!strcmp(argv[i], "--graph")) use_graph = 1;
+        else if (!strcmp(argv[i], "--no-wn-batch")) batch_wn = 0;
         else if (!strcmp(argv[i], "--verbose")) g_verbose = 1;
         else if (!strcmp(argv[i], "--fp32")) tf32 = 0;
         else {
@@ -497,6 +499,12 @@ int main(int argc, char** argv)
         stage_batch(m, images, n_images);
         dp_draw_levels(m);
         dp_inputs(m, &ctx);
+        /* Forced weight normalisation: the modules normalise one weight per launch (28 forward and
+           28 backward launches).  Step 1 records which weights they touch; from step 2 on every
+           weight is normalised by one launch here, the modules' own calls return at once, and the
+           backward calls are queued and run as one launch after the backward pass. */
+        if (batch_wn)
+            b200_wn_batch_mode(step == 1 ? 1 : 2);
         if (graph_exec) {
             NN_CUDA_CHECK(cudaGraphLaunch(graph_exec, ctx.stream));
         } else {
@@ -505,7 +513,11 @@ int main(int argc, char** argv)
             const int capture = use_graph && step == warmup;
             if (capture)
                 NN_CUDA_CHECK(cudaStreamBeginCapture(ctx.stream, cudaStreamCaptureModeThreadLocal));
+            if (batch_wn && step > 1)
+                b200_wn_forward_all(ctx.stream);
             dp_forward_backward(m, &ctx);
+            if (batch_wn && step > 1)
+                b200_wn_backward_flush(ctx.stream);
             if (capture) {
                 cudaGraph_t graph = NULL;
                 NN_CUDA_CHECK(cudaStreamEndCapture(ctx.stream, &graph));
@@ -540,6 +552,7 @@ int main(int argc, char** argv)
     }
     NN_CUDA_CHECK(cudaEventRecord(ev1, ctx.stream));
     NN_CUDA_CHECK(cudaStreamSynchronize(ctx.stream));
+    b200_wn_batch_mode(0);
     TRACE("rank %d: all steps finished\n", rank);
     launches_timed = b200_launch_count() - launches_timed;
     float ms = 0.0f;

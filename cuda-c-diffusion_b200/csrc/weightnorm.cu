@@ -16,6 +16,8 @@
 #include "../../include/b200_layer_kernels.h"
 
 #include <cooperative_groups.h>
+#include <mutex>
+#include <vector>
 
 namespace cg = cooperative_groups;
 
@@ -123,16 +125,44 @@ __global__ void __launch_bounds__(WN_THREADS) wn_forward_cluster(const WnTable t
     cluster.sync();
 }
 
-// single matrix; gW <- gain * (gW - dot_j * Wn), *g_gain += sum_j dot_j
-__global__ void __launch_bounds__(WN_THREADS) wn_backward_cluster(float* __restrict__ gW, const float* __restrict__ Wn,
-    const float* __restrict__ gain, float* __restrict__ g_gain, const int in, const int out)
+struct WnGradTable {
+    float* gW[B200_MAX_MULTI];
+    const float* Wn[B200_MAX_MULTI];
+    const float* gain[B200_MAX_MULTI];
+    float* g_gain[B200_MAX_MULTI];
+    int in[B200_MAX_MULTI];
+    int out[B200_MAX_MULTI];
+    int strip0[B200_MAX_MULTI + 1];
+    int count;
+};
+
+__device__ __forceinline__ int wn_find_grad(const WnGradTable& tb, int strip)
+{
+    int lo = 0, hi = tb.count - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tb.strip0[mid] <= strip)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    return lo;
+}
+
+// table of matrices; per matrix: gW <- gain * (gW - dot_j * Wn), *g_gain += sum_j dot_j
+// grid = (CS, total strips), cluster = (CS,1,1)
+__global__ void __launch_bounds__(WN_THREADS) wn_backward_cluster(const WnGradTable tb)
 {
     __shared__ float fold[32][WN_COLS + 1];
     __shared__ float colsum[WN_COLS];
     __shared__ float coldot[WN_COLS];
     cg::cluster_group cluster = cg::this_cluster();
     const int CS = gridDim.x, rank = blockIdx.x;
-    const int col0 = blockIdx.y * WN_COLS;
+    const int m = wn_find_grad(tb, blockIdx.y);
+    const int in = tb.in[m], out = tb.out[m];
+    float* __restrict__ gW = tb.gW[m];
+    const float* __restrict__ Wn = tb.Wn[m];
+    const int col0 = (blockIdx.y - tb.strip0[m]) * WN_COLS;
     const int qc = threadIdx.x & 7, rl = threadIdx.x >> 3;
     const int col = col0 + 4 * qc;
     const int rows_per = (in + CS - 1) / CS;
@@ -172,11 +202,11 @@ __global__ void __launch_bounds__(WN_THREADS) wn_backward_cluster(float* __restr
         if (rank == 0) {
             const float strip = warp_sum((col0 + (int)threadIdx.x < out) ? tot : 0.0f);
             if (threadIdx.x == 0)
-                atomicAdd(g_gain, strip);
+                atomicAdd(tb.g_gain[m], strip);
         }
     }
     __syncthreads();
-    const float gn = __ldg(gain);
+    const float gn = __ldg(tb.gain[m]);
     const float d0 = coldot[4 * qc], d1 = coldot[4 * qc + 1], d2 = coldot[4 * qc + 2], d3 = coldot[4 * qc + 3];
 #pragma unroll
     for (int j = 0; j < WN_VMAX; ++j) {
@@ -267,15 +297,67 @@ static void wn_launch_cluster_fwd(const WnTable& tb, int cs, float eps, cudaStre
     count_launch();
 }
 
+static void wn_launch_cluster_bwd(const WnGradTable& tb, int cs, cudaStream_t s)
+{
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3((unsigned)cs, (unsigned)tb.strip0[tb.count], 1);
+    cfg.blockDim = dim3(WN_THREADS, 1, 1);
+    cfg.stream = s;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, wn_backward_cluster, tb);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        report_error(__FILE__, __LINE__, "weight_normalize_backward launch failed: %s", cudaGetErrorString(e));
+        return;
+    }
+    count_launch();
+}
+
+// --- batching session (b200_wn_batch_mode) -----------------------------------
+struct WnSession {
+    std::mutex mu;
+    int mode = 0;
+    float eps = 0.0f;
+    std::vector<B200WeightDesc> fwd;       // recorded in mode 1, one entry per W
+    std::vector<B200WeightGradDesc> bwd;   // queued in mode 2
+};
+static WnSession g_wn;
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
 
+static void weight_normalize_now(float* W, int in, int out, float eps, cudaStream_t s);
+
 void launch_weight_normalize(float* W, int in, int out, float eps, cudaStream_t s)
 {
     B200_REQUIRE(in > 0 && out > 0, "weight_normalize: in=%d out=%d", in, out);
+    {
+        std::lock_guard<std::mutex> lk(g_wn.mu);
+        if (g_wn.mode == 2)
+            return;  // the driver normalises every recorded weight itself (b200_wn_forward_all)
+        if (g_wn.mode == 1) {
+            bool seen = false;
+            for (const B200WeightDesc& d : g_wn.fwd)
+                seen = seen || d.W == W;
+            if (!seen)
+                g_wn.fwd.push_back(B200WeightDesc{ W, in, out });
+            g_wn.eps = eps;
+        }
+    }
+    weight_normalize_now(W, in, out, eps, s);
+}
+
+static void weight_normalize_now(float* W, int in, int out, float eps, cudaStream_t s)
+{
     if (wn_cluster_ok(W, in, out) && !tune_get("wn_force_strip", 0)) {
         WnTable tb;
         tb.count = 1;
@@ -302,7 +384,7 @@ void launch_weight_normalize_multi(const B200WeightDesc* items, int count, float
         B200_REQUIRE(items[i].in > 0 && items[i].out > 0, "weight_normalize_multi: item %d in=%d out=%d", i,
             items[i].in, items[i].out);
         if (!wn_cluster_ok(items[i].W, items[i].in, items[i].out)) {
-            launch_weight_normalize(items[i].W, items[i].in, items[i].out, eps, s);
+            weight_normalize_now(items[i].W, items[i].in, items[i].out, eps, s);
             continue;
         }
         const int k = tb.count++;
@@ -319,35 +401,106 @@ void launch_weight_normalize_multi(const B200WeightDesc* items, int count, float
         wn_launch_cluster_fwd(tb, 8, eps, s);
 }
 
-void launch_weight_normalize_backward(float* gW, const float* Wn, const float* gain, float* g_gain, int in,
-    int out, cudaStream_t s)
+static void weight_normalize_backward_now(float* gW, const float* Wn, const float* gain, float* g_gain, int in, int out,
+    cudaStream_t s)
 {
-    B200_REQUIRE(in > 0 && out > 0, "weight_normalize_backward: in=%d out=%d", in, out);
     if (wn_cluster_ok(gW, in, out) && aligned16(Wn) && !tune_get("wn_force_strip", 0)) {
-        const int cs = wn_cluster_size(in);
-        cudaLaunchConfig_t cfg = {};
-        cudaLaunchAttribute attr[1];
-        cfg.gridDim = dim3((unsigned)cs, (unsigned)((out + WN_COLS - 1) / WN_COLS), 1);
-        cfg.blockDim = dim3(WN_THREADS, 1, 1);
-        cfg.stream = s;
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)cs;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, wn_backward_cluster, gW, Wn, gain, g_gain, in, out);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();
-            report_error(__FILE__, __LINE__, "weight_normalize_backward launch failed: %s", cudaGetErrorString(e));
-            return;
-        }
-        count_launch();
+        WnGradTable tb;
+        tb.count = 1;
+        tb.gW[0] = gW;
+        tb.Wn[0] = Wn;
+        tb.gain[0] = gain;
+        tb.g_gain[0] = g_gain;
+        tb.in[0] = in;
+        tb.out[0] = out;
+        tb.strip0[0] = 0;
+        tb.strip0[1] = (out + WN_COLS - 1) / WN_COLS;
+        wn_launch_cluster_bwd(tb, wn_cluster_size(in), s);
         return;
     }
     wn_strip<1><<<(out + 31) / 32, dim3(32, 8), 0, s>>>(gW, Wn, gain, g_gain, in, out, 0.0f);
     count_launch();
     B200_CHECK_LAUNCH();
+}
+
+void launch_weight_normalize_backward(float* gW, const float* Wn, const float* gain, float* g_gain, int in,
+    int out, cudaStream_t s)
+{
+    B200_REQUIRE(in > 0 && out > 0, "weight_normalize_backward: in=%d out=%d", in, out);
+    {
+        std::lock_guard<std::mutex> lk(g_wn.mu);
+        if (g_wn.mode == 2) {
+            g_wn.bwd.push_back(B200WeightGradDesc{ gW, Wn, gain, g_gain, in, out });
+            return;
+        }
+    }
+    weight_normalize_backward_now(gW, Wn, gain, g_gain, in, out, s);
+}
+
+void launch_weight_normalize_backward_multi(const B200WeightGradDesc* items, int count, cudaStream_t s)
+{
+    B200_REQUIRE(count >= 0 && (count == 0 || items), "weight_normalize_backward_multi: count=%d", count);
+    WnGradTable tb;
+    tb.count = 0;
+    tb.strip0[0] = 0;
+    for (int i = 0; i < count; ++i) {
+        const B200WeightGradDesc& d = items[i];
+        B200_REQUIRE(d.in > 0 && d.out > 0, "weight_normalize_backward_multi: item %d in=%d out=%d", i, d.in, d.out);
+        if (!(wn_cluster_ok(d.gW, d.in, d.out) && aligned16(d.Wn)) || tune_get("wn_force_strip", 0)) {
+            weight_normalize_backward_now(d.gW, d.Wn, d.gain, d.g_gain, d.in, d.out, s);
+            continue;
+        }
+        const int k = tb.count++;
+        tb.gW[k] = d.gW;
+        tb.Wn[k] = d.Wn;
+        tb.gain[k] = d.gain;
+        tb.g_gain[k] = d.g_gain;
+        tb.in[k] = d.in;
+        tb.out[k] = d.out;
+        tb.strip0[k + 1] = tb.strip0[k] + (d.out + WN_COLS - 1) / WN_COLS;
+        if (tb.count == B200_MAX_MULTI) {
+            wn_launch_cluster_bwd(tb, 8, s);
+            tb.count = 0;
+        }
+    }
+    if (tb.count > 0)
+        wn_launch_cluster_bwd(tb, 8, s);
+}
+
+void b200_wn_batch_mode(int mode)
+{
+    std::lock_guard<std::mutex> lk(g_wn.mu);
+    if (mode == 1 && g_wn.mode != 1)
+        g_wn.fwd.clear();
+    if (mode != 2)
+        g_wn.bwd.clear();
+    g_wn.mode = mode < 0 || mode > 2 ? 0 : mode;
+}
+
+int b200_wn_forward_all(cudaStream_t s)
+{
+    std::vector<B200WeightDesc> items;
+    float eps;
+    {
+        std::lock_guard<std::mutex> lk(g_wn.mu);
+        items = g_wn.fwd;
+        eps = g_wn.eps;
+    }
+    if (!items.empty())
+        launch_weight_normalize_multi(items.data(), (int)items.size(), eps, s);
+    return (int)items.size();
+}
+
+int b200_wn_backward_flush(cudaStream_t s)
+{
+    std::vector<B200WeightGradDesc> items;
+    {
+        std::lock_guard<std::mutex> lk(g_wn.mu);
+        items.swap(g_wn.bwd);
+    }
+    if (!items.empty())
+        launch_weight_normalize_backward_multi(items.data(), (int)items.size(), s);
+    return (int)items.size();
 }
 
 }  // extern "C"

@@ -205,6 +205,33 @@ typedef struct {
 } B200WeightDesc;
 void launch_weight_normalize_multi(const B200WeightDesc* items, int count, float eps, cudaStream_t s);
 
+/* launch_weight_normalize_backward (nn.h:394, kernels.cu:277-297, :337) for several weights in one launch.
+   Same per-weight semantics: gW <- gain * (gW - dot_j * Wn) per column j, *g_gain += sum_j dot_j
+   (the caller zeroes g_gain, as conv2d.c:50 and mp_linear.c:31 do). */
+typedef struct {
+    float* gW;
+    const float* Wn;
+    const float* gain;
+    float* g_gain;
+    int in, out;
+} B200WeightGradDesc;
+void launch_weight_normalize_backward_multi(const B200WeightGradDesc* items, int count, cudaStream_t s);
+
+/* Batching of the per-weight calls for hosts whose modules call launch_weight_normalize /
+   launch_weight_normalize_backward one weight at a time (conv2d.c, mp_linear.c, attention.c) and whose
+   driver owns the training step.  Modes:
+     0  off (default).
+     1  record: calls execute as usual; the forward calls' (W, in, out, eps) are remembered (one entry per W).
+     2  batched: launch_weight_normalize returns at once - the driver has normalised every recorded weight
+        with b200_wn_forward_all since the last parameter update; launch_weight_normalize_backward only
+        queues its arguments, and b200_wn_backward_flush runs the queue as one launch.  Nothing between a
+        module's backward and the optimizer reads gW or g_gain, so the deferral does not change results.
+   The state is per process, not per stream: one training loop at a time.  b200_wn_forward_all and
+   b200_wn_backward_flush return the number of weights they covered (0 when nothing is recorded/queued). */
+void b200_wn_batch_mode(int mode);
+int b200_wn_forward_all(cudaStream_t s);
+int b200_wn_backward_flush(cudaStream_t s);
+
 /* out[r,:] = wa[r]*a[r,:] + wb[r]*b[r,:] with per-row DEVICE coefficients: one
    launch for the per-sample launch_weighted_sum loops of diffusion/edm.c:56-64,
    :75-80, :205-207 and loss.c:65-70.  Aliasing as for launch_weighted_sum. */

@@ -18,7 +18,7 @@ def _code(arg):
         return ""
     if "cudaStream_t" in arg:
         return "s"
-    if "B200ParamUpdate" in arg or "B200WeightDesc" in arg or "char*" in arg:
+    if "B200ParamUpdate" in arg or "B200WeightDesc" in arg or "B200WeightGradDesc" in arg or "char*" in arg:
         return "h"
     if "*" in arg:
         return "p"

@@ -306,6 +306,73 @@ def test_multi_tensor_entry_points(pkg, lib, orc):
         assert cases.rel_err(t.cpu().numpy(), orc.weight_normalize(w, 1e-4)) <= 1e-5
 
 
+def test_weight_normalize_backward_multi_and_batching_session(lib, capi):
+    """One launch for several weights equals the per-weight launches; the record / batched session
+    (what a training loop over the reference's unmodified modules uses) gives the same results."""
+    import torch
+    rng = np.random.default_rng(77)
+    shapes = [(1152, 128), (64, 128), (576, 64), (128, 128), (9, 64), (30, 6)]
+    W = [_t(rng.standard_normal(s, dtype=np.float32)) for s in shapes]
+    for w, (i, o) in zip(W, shapes):
+        lib.launch_weight_normalize(_pp(w), i, o, ctypes.c_float(1e-4), _st())
+    G0 = [_t(rng.standard_normal(s, dtype=np.float32)) for s in shapes]
+    gains = [_t(np.array([0.5 + 0.25 * k], np.float32)) for k in range(len(shapes))]
+
+    def single():
+        g = [x.clone() for x in G0]
+        gg = [torch.zeros(1, device="cuda") for _ in shapes]
+        for k, (i, o) in enumerate(shapes):
+            lib.launch_weight_normalize_backward(_pp(g[k]), _pp(W[k]), _pp(gains[k]), _pp(gg[k]), i, o, _st())
+        torch.cuda.synchronize()
+        return g, gg
+
+    ref_g, ref_gg = single()
+    g = [x.clone() for x in G0]
+    gg = [torch.zeros(1, device="cuda") for _ in shapes]
+    arr = (capi.WeightGradDesc * len(shapes))()
+    for k, (i, o) in enumerate(shapes):
+        arr[k] = capi.WeightGradDesc(g[k].data_ptr(), W[k].data_ptr(), gains[k].data_ptr(), gg[k].data_ptr(), i, o)
+    n0 = lib.b200_launch_count()
+    lib.launch_weight_normalize_backward_multi(ctypes.cast(arr, ctypes.c_void_p), len(shapes), _st())
+    torch.cuda.synchronize()
+    assert lib.b200_launch_count() - n0 == 2  # one table launch + the one shape (30x6) outside the cluster kernel
+    for k in range(len(shapes)):
+        # (the table launch uses clusters of 8 for every matrix, so column dots fold in another order)
+        assert cases.rel_err(g[k].cpu().numpy(), ref_g[k].cpu().numpy()) <= 2e-6, k
+        assert abs(float(gg[k]) - float(ref_gg[k])) <= 1e-5 * max(1.0, abs(float(ref_gg[k]))), k
+
+    # session: record one pass, then batched passes
+    try:
+        raw = [_t(rng.standard_normal(s, dtype=np.float32)) for s in shapes]
+        expect = [x.clone() for x in raw]
+        for w, (i, o) in zip(expect, shapes):
+            lib.launch_weight_normalize(_pp(w), i, o, ctypes.c_float(1e-4), _st())
+        lib.b200_wn_batch_mode(1)
+        scratch = [x.clone() for x in raw]
+        for w, (i, o) in zip(scratch, shapes):
+            lib.launch_weight_normalize(_pp(w), i, o, ctypes.c_float(1e-4), _st())
+        lib.b200_wn_batch_mode(2)
+        for w, x in zip(scratch, raw):
+            w.copy_(x)  # "the optimizer changed the weights"
+        assert lib.b200_wn_forward_all(_st()) == len(shapes)
+        n0 = lib.b200_launch_count()
+        for w, (i, o) in zip(scratch, shapes):  # the modules' own calls are no-ops now
+            lib.launch_weight_normalize(_pp(w), i, o, ctypes.c_float(1e-4), _st())
+        g2 = [x.clone() for x in G0]
+        gg2 = [torch.zeros(1, device="cuda") for _ in shapes]
+        for k, (i, o) in enumerate(shapes):  # queued, not launched
+            lib.launch_weight_normalize_backward(_pp(g2[k]), _pp(W[k]), _pp(gains[k]), _pp(gg2[k]), i, o, _st())
+        assert lib.b200_launch_count() == n0
+        assert lib.b200_wn_backward_flush(_st()) == len(shapes)
+        assert lib.b200_wn_backward_flush(_st()) == 0
+        torch.cuda.synchronize()
+        for k in range(len(shapes)):
+            assert cases.rel_err(scratch[k].cpu().numpy(), expect[k].cpu().numpy()) <= 1e-6, k
+            assert cases.rel_err(g2[k].cpu().numpy(), ref_g[k].cpu().numpy()) <= 2e-6, k
+    finally:
+        lib.b200_wn_batch_mode(0)
+
+
 def test_axpby_rows_matches_per_sample_loop(lib, orc):
     import torch
     rng = np.random.default_rng(51)
