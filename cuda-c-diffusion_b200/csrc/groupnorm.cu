@@ -626,6 +626,7 @@ __global__ void __launch_bounds__(GN_THREADS, 2) gn_bwd_tile(const __grid_consta
 }  // namespace b200
 
 #include "groupnorm_strip.cuh"
+#include "groupnorm_cstrip.cuh"
 
 namespace b200 {
 
@@ -1053,11 +1054,107 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
     }
 }
 
+// Chunked strips for samples too tall for the register-resident strips: 512 threads, strip width Ct =
+// the narrowest whole-group width with runs of at least 64 bytes (more strips, smaller L2 footprint).
+static bool cstrip_plan(StripPlan* out, int HW, int C, int G)
+{
+    if (C % 4 != 0 || C % G != 0)
+        return false;
+    const int NT = 512, cpg = C / G;
+    int best = 0;
+    for (int Ct = 4; Ct <= C && Ct <= 512; Ct += 4) {
+        if (C % Ct != 0 || Ct % cpg != 0 || NT % (Ct / 4) != 0)
+            continue;
+        if (best == 0 || (best * 4 < 64 && Ct > best))
+            best = Ct;
+    }
+    if (best == 0)
+        return false;
+    StripGeom g;
+    g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = best; g.Q = best / 4; g.RSTEP = NT / g.Q;
+    g.Gt = best / cpg; g.nct = C / best;
+    g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+    out->NT = NT;
+    out->VPT = 0;
+    out->g = g;
+    const int red = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * (NT / 32) * best : 2 * NT * 4;
+    out->smem = (size_t)(red + 2 * best + 2 * g.Gt) * sizeof(float);
+    return true;
+}
+
+template <int ACT>
+static bool gn_forward_cstrip(float* y, float* mu, float* rstd, const float* x, const float* gamma,
+    const float* beta, int B, int HW, int C, int G, float eps, cudaStream_t s)
+{
+    if constexpr (ACT != ACT_IDENTITY && ACT != ACT_SILU && ACT != ACT_MP_SILU) {
+        return false;
+    } else {
+        if (tune_get("gn_force_generic", 0) || tune_get("gn_no_cstrip", 0))
+            return false;
+        if (!(aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)) || (long)B * HW * C >= 2147483648L)
+            return false;
+        StripPlan plan;
+        if (!cstrip_plan(&plan, HW, C, G))
+            return false;
+        constexpr int VPT = 4, MB = 2;
+        const long items = (long)B * plan.g.nct;
+        const long resident = (long)sm_count() * MB;
+        const long per_cta = (items + resident - 1) / resident;
+        const long pgrid = (items + per_cta - 1) / per_cta;
+        const int nchunks = (HW + plan.g.RSTEP * VPT - 1) / (plan.g.RSTEP * VPT);
+        const size_t psmem = (size_t)VPT * plan.NT * 16 + plan.smem;
+        static bool done[64] = { false };
+        return pstrip_launch(gn_fwd_cstrip<512, VPT, ACT, MB>, done, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
+            plan.g, eps, (int)items, nchunks);
+    }
+}
+
+template <int ACT>
+static bool gn_backward_cstrip(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+    const float* gamma, const float* beta, const float* mu, const float* rstd, int B, int HW, int C, int G,
+    cudaStream_t s)
+{
+    if constexpr (ACT != ACT_IDENTITY && ACT != ACT_SILU && ACT != ACT_MP_SILU) {
+        return false;
+    } else {
+        if (tune_get("gn_force_generic", 0) || tune_get("gn_no_cstrip", 0))
+            return false;
+        if (!(aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(gamma)) || (long)B * HW * C >= 2147483648L)
+            return false;
+        if (ACT != ACT_IDENTITY && !aligned16(beta))
+            return false;
+        StripPlan plan;
+        if (!cstrip_plan(&plan, HW, C, G))
+            return false;
+        Scratch sc;
+        if (!scratch_get(s, (size_t)2 * B * C, 0, &sc))
+            return false;
+        // 8 rows per tensor and thread at one CTA per SM (128 registers), or 4 rows at two CTAs per SM (64
+        // registers, some spills in the SiLU variants)
+        const int VPT = tune_get("gn_bwd_cstrip_vpt", 8) == 4 ? 4 : 8, MB = VPT == 4 ? 2 : 1;
+        const long items = (long)B * plan.g.nct;
+        const long resident = (long)sm_count() * MB;
+        const long per_cta = (items + resident - 1) / resident;
+        const long pgrid = (items + per_cta - 1) / per_cta;
+        const int nchunks = (HW + plan.g.RSTEP * VPT - 1) / (plan.g.RSTEP * VPT);
+        const size_t psmem = (size_t)2 * VPT * plan.NT * 16 + plan.smem;
+        static bool done4[64] = { false }, done8[64] = { false };
+        const bool ok = VPT == 4
+            ? pstrip_launch(gn_bwd_cstrip<512, 4, ACT, 2>, done4, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
+                  mu, rstd, plan.g, (int)items, nchunks)
+            : pstrip_launch(gn_bwd_cstrip<512, 8, ACT, 1>, done8, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
+                  mu, rstd, plan.g, (int)items, nchunks);
+        return ok && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
+    }
+}
+
 template <int ACT>
 static void gn_forward(float* y, float* mu, float* rstd, const float* x, const float* gamma, const float* beta,
     int B, int HW, int C, int G, float eps, cudaStream_t s)
 {
     if (gn_forward_strip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
+        return;
+    if (gn_forward_cstrip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
     if (gn_forward_tile<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
@@ -1118,6 +1215,8 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     cudaStream_t s)
 {
     if (gn_backward_strip<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
+        return;
+    if (gn_backward_cstrip<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
         return;
     if (gn_backward_tile<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
         return;
