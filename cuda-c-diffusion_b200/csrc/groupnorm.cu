@@ -968,6 +968,18 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
                    dy, x, gamma, beta, mu, rstd, plan.g, B)                                                \
             && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
 
+static bool cstrip_plan(StripPlan* out, int HW, int C, int G);
+
+// A register-resident plan whose runs are shorter than 64 bytes only exists because the sample is tall;
+// the chunked strips keep 64-byte runs for such samples and are preferred when they apply.
+static bool strip_too_narrow(const StripPlan& plan, int HW, int C, int G)
+{
+    if (plan.g.Ct * 4 >= 64 || tune_get("gn_no_cstrip", 0))
+        return false;
+    StripPlan wide;
+    return cstrip_plan(&wide, HW, C, G) && wide.g.Ct > plan.g.Ct;
+}
+
 template <int ACT>
 static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, const float* gamma,
     const float* beta, int B, int HW, int C, int G, float eps, cudaStream_t s)
@@ -981,6 +993,8 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
             return false;
         StripPlan plan;
         if (!strip_plan(&plan, B, HW, C, G, 8, tune_get("gn_fwd_strip_ct", 0), tune_get("gn_fwd_strip_nt", 0), 0))
+            return false;
+        if (!tune_get("gn_fwd_strip_ct", 0) && strip_too_narrow(plan, HW, C, G))
             return false;
         const long grid = (long)B * plan.g.nct;
         if (grid > 2147483647L)
@@ -1028,6 +1042,8 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
         if (!strip_plan(&plan, B, HW, C, G, max_vpt, tune_get("gn_bwd_strip_ct", 0), force_nt, max_vpt == 8 ? 1 : 0))
             return false;
         if (plan.VPT == 8 && plan.NT != 512)
+            return false;
+        if (!tune_get("gn_bwd_strip_ct", 0) && strip_too_narrow(plan, HW, C, G))
             return false;
         const long grid = (long)B * plan.g.nct;
         if (grid > 2147483647L)

@@ -254,6 +254,31 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
     _check(got, ref, f"strip nt{nt}")
 
 
+@pytest.mark.parametrize("shape", [dict(B=3, HW=4096, C=32, G=8), dict(B=2, HW=2500, C=48, G=6),
+                                   dict(B=80, HW=4100, C=64, G=32)])
+@pytest.mark.parametrize("act", ["silu", None])
+@pytest.mark.parametrize("bwd_vpt", [8, 4])
+def test_groupnorm_chunked_strips_for_tall_samples(lib, orc, shape, act, bwd_vpt):
+    """Samples too tall for the register-resident strips (64x64 images, ragged 50x50, and enough strips
+    that every CTA loops over several): the chunked two-pass strip kernels are taken, not the tile kernels."""
+    p = dict(shape, act=act)
+    inp = cases.make_inputs("groupnorm", p, seed=41)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    lib.b200_tune_set(b"gn_no_tile", 1)
+    lib.b200_tune_set(b"gn_bwd_cstrip_vpt", bwd_vpt)
+    try:
+        n0 = lib.b200_launch_count()
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+        assert lib.b200_launch_count() - n0 == 3, "expected chunked forward, chunked backward and the fold kernel"
+        got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        lib.b200_tune_set(b"gn_no_tile", 0)
+        lib.b200_tune_set(b"gn_bwd_cstrip_vpt", 8)
+    _check(got, ref, "chunked strips")
+    for k in got:
+        assert np.array_equal(got[k], got2[k]), k
+
+
 @pytest.mark.parametrize("bwd_pipeline", [0, 1])
 def test_groupnorm_pipelined_strips(lib, orc, bwd_pipeline):
     """Many more strips than resident CTAs: the persistent kernels that prefetch the next strip with
