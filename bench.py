@@ -319,7 +319,8 @@ def e2e_steps(step, steps, warmup, world):
 # ------------------------------------------------------------------------------------ per-op table
 def graph_time(lib, fn, nsets, reps, scratch_bytes=0):
     """Average device time of fn(i) over `reps` launches replayed from a CUDA graph
-    (removes host launch overhead; fn cycles through `nsets` buffer sets larger than L2)."""
+    (removes host launch overhead; fn cycles through `nsets` buffer sets larger than L2).
+    The graph is replayed once untimed (warm-up of `reps` launches) and once timed."""
     s = torch.cuda.Stream()
     if scratch_bytes and hasattr(lib, "b200_scratch_reserve"):
         lib.b200_scratch_reserve(ctypes.c_void_p(s.cuda_stream), ctypes.c_longlong(scratch_bytes))
@@ -367,8 +368,8 @@ def ops_table(lib, fused, peak):
     dg, db = torch.empty(c, device=dev), torch.empty(c, device=dev)
     fw = lambda i: lib.launch_groupnorm_forward(P(ys[i]), P(mu), P(rs), P(xs[i]), P(gam), P(bet), b, hw, c, g, F(1e-5), st())
     bw = lambda i: lib.launch_groupnorm_backward(P(ys[i]), P(dg), P(db), P(dys[i]), P(xs[i]), P(gam), P(mu), P(rs), b, hw, c, g, st())
-    add("cfg0_groupnorm_fwd", graph_time(lib, fw, ns, 40), 2 * n * 4)
-    add("cfg0_groupnorm_bwd", graph_time(lib, bw, ns, 40, 2 * b * c * 4), 3 * n * 4)
+    add("cfg0_groupnorm_fwd", graph_time(lib, fw, ns, 100), 2 * n * 4)
+    add("cfg0_groupnorm_bwd", graph_time(lib, bw, ns, 100, 2 * b * c * 4), 3 * n * 4)
     del xs, ys, dys
 
     # ---- config 1: EDM magnitude-preserving ops on [256,28,28,128]
@@ -378,33 +379,33 @@ def ops_table(lib, fused, peak):
     A = [torch.randn(n, device=dev) for _ in range(ns)]
     Bb = [torch.randn(n, device=dev) for _ in range(ns)]
     O = [torch.empty(n, device=dev) for _ in range(ns)]
-    add("cfg1_mp_silu_fwd", graph_time(lib, lambda i: lib.launch_activation_forward(P(O[i]), P(A[i]), n, 5, st()), ns, 20), 2 * n * 4)
-    add("cfg1_mp_silu_bwd", graph_time(lib, lambda i: lib.launch_activation_backward(P(O[i]), P(Bb[i]), P(A[i]), n, 5, st()), ns, 20), 3 * n * 4)
-    add("cfg1_mp_sum_fwd", graph_time(lib, lambda i: lib.launch_mp_sum(P(O[i]), P(A[i]), P(Bb[i]), F(0.3), n, st()), ns, 20), 3 * n * 4)
+    add("cfg1_mp_silu_fwd", graph_time(lib, lambda i: lib.launch_activation_forward(P(O[i]), P(A[i]), n, 5, st()), ns, 100), 2 * n * 4)
+    add("cfg1_mp_silu_bwd", graph_time(lib, lambda i: lib.launch_activation_backward(P(O[i]), P(Bb[i]), P(A[i]), n, 5, st()), ns, 100), 3 * n * 4)
+    add("cfg1_mp_sum_fwd", graph_time(lib, lambda i: lib.launch_mp_sum(P(O[i]), P(A[i]), P(Bb[i]), F(0.3), n, st()), ns, 100), 3 * n * 4)
     if fused:
-        add("cfg1_mp_sum_bwd", graph_time(lib, lambda i: lib.launch_mp_sum_backward(P(O[i]), P(Bb[i]), P(A[i]), F(0.3), n, st()), ns, 20), 3 * n * 4)
+        add("cfg1_mp_sum_bwd", graph_time(lib, lambda i: lib.launch_mp_sum_backward(P(O[i]), P(Bb[i]), P(A[i]), F(0.3), n, st()), ns, 100), 3 * n * 4)
     else:
         def two(i):
             lib.launch_weighted_sum(P(O[i]), P(A[i]), P(A[i]), F(0.919), F(0.0), n, st())
             lib.launch_weighted_sum(P(Bb[i]), P(A[i]), P(A[i]), F(0.394), F(0.0), n, st())
-        add("cfg1_mp_sum_bwd", graph_time(lib, two, ns, 20), 3 * n * 4)
-    add("cfg1_mp_cat_fwd", graph_time(lib, lambda i: lib.launch_mp_channel_cat(P(O[i]), P(A[i]), P(Bb[i]), F(0.5), rows, 64, 64, st()), ns, 20), 2 * n * 4)
-    add("cfg1_mp_cat_bwd", graph_time(lib, lambda i: lib.launch_mp_channel_split(P(A[i]), P(Bb[i]), P(O[i]), F(0.5), rows, 64, 64, st()), ns, 20), 2 * n * 4)
+        add("cfg1_mp_sum_bwd", graph_time(lib, two, ns, 100), 3 * n * 4)
+    add("cfg1_mp_cat_fwd", graph_time(lib, lambda i: lib.launch_mp_channel_cat(P(O[i]), P(A[i]), P(Bb[i]), F(0.5), rows, 64, 64, st()), ns, 100), 2 * n * 4)
+    add("cfg1_mp_cat_bwd", graph_time(lib, lambda i: lib.launch_mp_channel_split(P(A[i]), P(Bb[i]), P(O[i]), F(0.5), rows, 64, 64, st()), ns, 100), 2 * n * 4)
     if fused:  # pixel norm has no counterpart in the reference
-        add("cfg1_pixel_norm_fwd", graph_time(lib, lambda i: lib.launch_pixel_norm_forward(P(O[i]), P(A[i]), rows, 128, F(1e-4), st()), ns, 20), 2 * n * 4)
-        add("cfg1_pixel_norm_bwd", graph_time(lib, lambda i: lib.launch_pixel_norm_backward(P(O[i]), P(Bb[i]), P(A[i]), rows, 128, F(1e-4), st()), ns, 20), 3 * n * 4)
+        add("cfg1_pixel_norm_fwd", graph_time(lib, lambda i: lib.launch_pixel_norm_forward(P(O[i]), P(A[i]), rows, 128, F(1e-4), st()), ns, 100), 2 * n * 4)
+        add("cfg1_pixel_norm_bwd", graph_time(lib, lambda i: lib.launch_pixel_norm_backward(P(O[i]), P(Bb[i]), P(A[i]), rows, 128, F(1e-4), st()), ns, 100), 3 * n * 4)
     del A, Bb, O
     Wm, Mm = torch.randn(1152, 128, device=dev), torch.randn(1152, 128, device=dev)
     gain, gg = torch.ones(1, device=dev), torch.zeros(1, device=dev)
-    add("cfg1_weight_norm_fwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize(P(Wm), 1152, 128, F(1e-4), st()), 1, 50), 2 * Wm.numel() * 4)
-    add("cfg1_weight_norm_bwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize_backward(P(Mm), P(Wm), P(gain), P(gg), 1152, 128, st()), 1, 50), 3 * Wm.numel() * 4)
+    add("cfg1_weight_norm_fwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize(P(Wm), 1152, 128, F(1e-4), st()), 1, 100), 2 * Wm.numel() * 4)
+    add("cfg1_weight_norm_bwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize_backward(P(Mm), P(Wm), P(gain), P(gg), 1152, 128, st()), 1, 100), 3 * Wm.numel() * 4)
 
     # ---- embeddings (latency-bound)
     tt = torch.randint(0, 1000, (256,), device=dev).float(); e1 = torch.empty(256, 512, device=dev)
-    add("cfg2_sinusoidal_256x512", graph_time(lib, lambda i: lib.launch_sinusoidal(P(e1), P(tt), 256, 512, F(9.2103404), st()), 1, 50), e1.numel() * 4)
+    add("cfg2_sinusoidal_256x512", graph_time(lib, lambda i: lib.launch_sinusoidal(P(e1), P(tt), 256, 512, F(9.2103404), st()), 1, 100), e1.numel() * 4)
     xx, fr, ph = torch.randn(256, device=dev), torch.randn(128, device=dev), torch.rand(128, device=dev)
     e2 = torch.empty(256, 128, device=dev)
-    add("cfg3_mp_fourier_256x128", graph_time(lib, lambda i: lib.launch_mp_fourier(P(e2), P(xx), P(fr), P(ph), 256, 128, st()), 1, 50), e2.numel() * 4)
+    add("cfg3_mp_fourier_256x128", graph_time(lib, lambda i: lib.launch_mp_fourier(P(e2), P(xx), P(fr), P(ph), 256, 128, st()), 1, 100), e2.numel() * 4)
 
     # ---- config 4: optimizer, 64M parameters
     npar = 64 * 2 ** 20
@@ -412,13 +413,13 @@ def ops_table(lib, fused, peak):
     v_.abs_()
     hp = (F(1e-4), F(0.9), F(0.999), F(1e-8), F(0.19), F(0.002))
     if fused:
-        add("cfg4_adam_ema_fused_64M", graph_time(lib, lambda i: lib.launch_adam_ema_step(P(p_), P(m_), P(v_), P(s_), P(g_), *hp, F(0.999), F(1.0), ctypes.c_longlong(npar), st()), 1, 5), 36 * npar)
+        add("cfg4_adam_ema_fused_64M", graph_time(lib, lambda i: lib.launch_adam_ema_step(P(p_), P(m_), P(v_), P(s_), P(g_), *hp, F(0.999), F(1.0), ctypes.c_longlong(npar), st()), 1, 100), 36 * npar)
     else:
         def two_pass(i):
             lib.launch_adam_step(P(p_), P(m_), P(v_), P(g_), *hp, npar, st())
             lib.launch_weighted_sum(P(s_), P(s_), P(p_), F(0.999), F(0.001), npar, st())
-        add("cfg4_adam_then_ema_64M", graph_time(lib, two_pass, 1, 5), 36 * npar)
-    add("cfg4_adam_64M", graph_time(lib, lambda i: lib.launch_adam_step(P(p_), P(m_), P(v_), P(g_), *hp, npar, st()), 1, 5), 28 * npar)
+        add("cfg4_adam_then_ema_64M", graph_time(lib, two_pass, 1, 100), 36 * npar)
+    add("cfg4_adam_64M", graph_time(lib, lambda i: lib.launch_adam_step(P(p_), P(m_), P(v_), P(g_), *hp, npar, st()), 1, 100), 28 * npar)
     return out
 
 
