@@ -18,6 +18,9 @@
  *                     [--id-file PATH] [--seed S] [--log-every N] [--dump FILE]
  *   --dump FILE: rank 0 writes the last loss and all parameters (raw float32) after the run.
  *   --no-wn-batch: keep one weight-normalisation launch per weight (default: one launch for all).
+ *   --save FILE / --resume FILE: the reference's training checkpoint (checkpoint.c: parameters, EMA
+ *   shadows, Adam moments, step and Adam counters).  Rank 0 writes it after the last step; every rank
+ *   reads it before the first (replicas hold identical state, so no gather is involved).
  *   --graph: forward + backward are captured into one CUDA graph on the last warm-up step and
  *   replayed afterwards (uploads, noise, the gradient all-reduce and the update stay outside).
  *   RANK / WORLD_SIZE / LOCAL_RANK come from the environment (torchrun sets them).
@@ -404,6 +407,7 @@ int main(int argc, char** argv)
     unsigned seed = 410293;
     const char* id_file = "/tmp/edm_dp_train.ncclid";
     const char* dump_path = NULL;
+    const char *save_path = NULL, *resume_path = NULL;
     for (int i = 1; i < argc; ++i) {
         if (!strcmp(argv[i], "--steps") && i + 1 < argc) steps = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--warmup") && i + 1 < argc) warmup = atoi(argv[++i]);
@@ -412,6 +416,8 @@ int main(int argc, char** argv)
         else if (!strcmp(argv[i], "--id-file") && i + 1 < argc) id_file = argv[++i];
         else if (!strcmp(argv[i], "--log-every") && i + 1 < argc) log_every = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--dump") && i + 1 < argc) dump_path = argv[++i];
+        else if (!strcmp(argv[i], "--save") && i + 1 < argc) save_path = argv[++i];
+        else if (!strcmp(argv[i], "--resume") && i + 1 < argc) resume_path = argv[++i];
         else if (!strcmp(argv[i], "--check")) check = 1;
         else if (!strcmp(argv[i], "--graph")) use_graph = 1;
         else if (!strcmp(argv[i], "--no-wn-batch")) batch_wn = 0;
@@ -459,8 +465,24 @@ int main(int argc, char** argv)
     const float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, decay = 0.999f;
     Optimizer* opt = optimizer_adam(&params, lr, b1, b2, eps);
     EMA* ema = ema_create(&params, decay);
-    NN_CURAND_CHECK(curandSetGeneratorOffset(ctx.curand, (unsigned long long)(rank + 1) << 40));
-    srand(seed + 7919u * (unsigned)rank);
+    ParamList shadow_l, adam_m, adam_v;
+    param_list_init(&shadow_l);
+    param_list_init(&adam_m);
+    param_list_init(&adam_v);
+    ema_shadow_list(ema, &shadow_l);
+    optimizer_moment_lists(opt, &adam_m, &adam_v);
+    int first_step = 1;
+    if (resume_path) {
+        int loaded_step = 0, adam_t = 0;
+        if (checkpoint_load_training(resume_path, &loaded_step, &adam_t, &params, &shadow_l, &adam_m, &adam_v) != 0) {
+            fprintf(stderr, "rank %d: cannot load %s\n", rank, resume_path);
+            return 1;
+        }
+        optimizer_set_timestep(opt, adam_t);
+        first_step = loaded_step + 1;
+    }
+    NN_CURAND_CHECK(curandSetGeneratorOffset(ctx.curand, ((unsigned long long)(rank + 1) << 40) + ((unsigned long long)first_step << 24)));
+    srand(seed + 7919u * (unsigned)rank + 104729u * (unsigned)first_step);
     long n_params = 0;
     for (int i = 0; i < params.count; ++i)
         n_params += params.items[i].size;
@@ -494,7 +516,7 @@ int main(int argc, char** argv)
             launches_timed = b200_launch_count();
             NN_CUDA_CHECK(cudaEventRecord(ev0, ctx.stream));
         }
-        const float cur_lr = lr_inv_sqrt(lr, step, 500, 5000);
+        const float cur_lr = lr_inv_sqrt(lr, first_step - 1 + step, 500, 5000);
         dp_next_slot(m);
         stage_batch(m, images, n_images);
         dp_draw_levels(m);
@@ -550,6 +572,8 @@ int main(int argc, char** argv)
                 fprintf(stderr, "step %d loss %.6f lr %.2e\n", step, last_loss, cur_lr);
         }
     }
+    if (steps == 0) /* nothing was timed (state inspection: --resume ... --dump) */
+        NN_CUDA_CHECK(cudaEventRecord(ev0, ctx.stream));
     NN_CUDA_CHECK(cudaEventRecord(ev1, ctx.stream));
     NN_CUDA_CHECK(cudaStreamSynchronize(ctx.stream));
     b200_wn_batch_mode(0);
@@ -579,10 +603,18 @@ int main(int argc, char** argv)
                "\"steps\": %d, \"warmup\": %d, \"params\": %ld, \"param_tensors\": %d, \"tf32\": %d, "
                "\"library_launches_per_step\": %.1f, \"cuda_graph_nodes\": %zu, \"first_loss\": %.5f, \"last_loss\": %.5f, "
                "\"replicas_in_sync\": %s, \"b200_device_error\": %d}}\n",
-            (double)batch * world * steps / (h_stat[0] * 1e-3), h_stat[0] / steps, world, batch, steps, warmup, n_params,
-            params.count, tf32, (double)launches_timed / steps, graph_nodes, first_loss, last_loss, in_sync ? "true" : "false",
+            steps ? (double)batch * world * steps / (h_stat[0] * 1e-3) : 0.0, steps ? h_stat[0] / steps : 0.0, world, batch, steps, warmup, n_params,
+            params.count, tf32, steps ? (double)launches_timed / steps : 0.0, graph_nodes, first_loss, last_loss, in_sync ? "true" : "false",
             b200_device_error_status());
 
+    if (save_path && rank == 0) {
+        const int rc = checkpoint_save_training(save_path, first_step - 1 + warmup + steps, optimizer_timestep(opt), &params,
+            &shadow_l, &adam_m, &adam_v);
+        if (rc != 0) {
+            fprintf(stderr, "cannot write %s (%d)\n", save_path, rc);
+            return 1;
+        }
+    }
     if (dump_path && rank == 0) { /* last loss, then every parameter tensor, as raw float32 */
         FILE* f = fopen(dump_path, "wb");
         if (!f) {

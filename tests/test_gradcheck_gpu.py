@@ -104,3 +104,26 @@ def test_replaced_conv2d_trains_to_the_same_parameters(tmp_path):
     assert a.size == b.size and a.size > 1_000_000
     assert abs(a[0] - b[0]) <= 1e-5 * abs(a[0])                       # loss of the last step
     assert np.abs(a[1:] - b[1:]).max() <= 1e-5 * np.abs(a[1:]).max()  # every parameter
+
+
+def test_edm_dp_checkpoint_round_trip(tmp_path):
+    """--save writes the reference's training checkpoint after the run; --resume restores parameters
+    (and optimizer/EMA state) exactly and training continues from there."""
+    import json
+    import numpy as np
+    exe = ROOT / "oracle" / "_ref" / "edm_dp_train_fastconv"
+    if not exe.exists():
+        pytest.skip("edm_dp_train_fastconv not built (needs the reference sources at build time)")
+    ck, d_a, d_b, d_c = (str(tmp_path / n) for n in ("state.ckpt", "a.bin", "b.bin", "c.bin"))
+    run = lambda *a: subprocess.run([str(exe), "--fp32", "--batch", "8", *a], capture_output=True, text=True, timeout=300)
+    res = run("--warmup", "2", "--steps", "2", "--save", ck, "--dump", d_a)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    res = run("--resume", ck, "--warmup", "0", "--steps", "0", "--dump", d_b)  # load and dump, no training
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    a, b = np.fromfile(d_a, dtype=np.float32), np.fromfile(d_b, dtype=np.float32)
+    assert np.array_equal(a[1:], b[1:])
+    res = run("--resume", ck, "--warmup", "2", "--steps", "2", "--dump", d_c)  # continue for four more steps
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    got = json.loads(next(ln for ln in res.stdout.splitlines() if ln.startswith("{")))["edm_dp_train"]
+    c = np.fromfile(d_c, dtype=np.float32)
+    assert np.isfinite(c).all() and not np.array_equal(c[1:], a[1:]) and np.isfinite(got["last_loss"])
