@@ -372,7 +372,11 @@ static void exchange_id(ncclUniqueId* id, int rank, const char* path)
         rename(tmp, path);
         return;
     }
-    for (int tries = 0; tries < 1200; ++tries) { /* up to 60 s */
+    /* a peer that never shows up must not hang this rank: bounded wait on the host (default 60 s,
+       EDM_DP_ID_WAIT_S overrides), then a clear message and a non-zero exit; nothing is on the device yet */
+    const char* w = getenv("EDM_DP_ID_WAIT_S");
+    const double wait_s = (w && w[0]) ? atof(w) : 60.0;
+    for (int tries = 0; tries * 0.05 < wait_s; ++tries) {
         FILE* f = fopen(path, "rb");
         if (f) {
             const size_t got = fread(id, sizeof *id, 1, f);
@@ -382,7 +386,7 @@ static void exchange_id(ncclUniqueId* id, int rank, const char* path)
         }
         usleep(50000);
     }
-    fprintf(stderr, "rank %d: no NCCL id at %s after 60 s\n", rank, path);
+    fprintf(stderr, "rank %d: rank 0 did not publish the NCCL id at %s within %.1f s\n", rank, path, wait_s);
     exit(1);
 }
 

@@ -127,3 +127,20 @@ def test_edm_dp_checkpoint_round_trip(tmp_path):
     got = json.loads(next(ln for ln in res.stdout.splitlines() if ln.startswith("{")))["edm_dp_train"]
     c = np.fromfile(d_c, dtype=np.float32)
     assert np.isfinite(c).all() and not np.array_equal(c[1:], a[1:]) and np.isfinite(got["last_loss"])
+
+
+def test_edm_dp_missing_peer_ends_with_an_error_not_a_hang(tmp_path):
+    """Failure injected on the host: rank 1 of a world of two starts alone, so the NCCL id never appears.
+    The rank must give up after its bounded wait with a clear message; nothing has touched the device."""
+    import os
+    import time
+    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+    if not exe.exists():
+        pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="0", EDM_DP_ID_WAIT_S="1.5")
+    t0 = time.time()
+    res = subprocess.run([str(exe), "--batch", "8", "--steps", "1", "--warmup", "0", "--id-file", str(tmp_path / "never")],
+                         env=env, capture_output=True, text=True, timeout=120)
+    assert res.returncode != 0
+    assert "did not publish the NCCL id" in res.stderr
+    assert time.time() - t0 < 60

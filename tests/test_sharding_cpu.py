@@ -133,3 +133,76 @@ def test_world2_sharded_update_and_norm_grads_match_single_rank(n):
     _, mu, rstd = orc.layernorm_forward(x, gam, bet, 1e-5)
     _, dg, db = orc.layernorm_backward(dy, x, gam, mu, rstd)
     assert np.allclose(out["dg"], dg, rtol=1e-5, atol=1e-6) and np.allclose(out["db"], db, rtol=1e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------- failures, injected on the host
+def test_bad_rank_and_world_are_rejected():
+    sh = _sharding()
+    for fn in (sh.batch_shard, sh.param_range):
+        with pytest.raises(ValueError):
+            fn(10, 2, 2)
+        with pytest.raises(ValueError):
+            fn(10, -1, 2)
+
+
+def _lonely_worker(port, q):
+    """World of two in which the second rank never starts: the rendezvous must end with an error after
+    the short timeout instead of waiting forever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        q.put("joined")
+    except Exception as exc:  # noqa: BLE001 - any rendezvous error is the expected outcome
+        q.put("error: " + type(exc).__name__)
+
+
+def test_rank_that_never_joins_ends_in_a_timeout_not_a_hang():
+    with socket.socket() as s_:
+        s_.bind(("127.0.0.1", 0))
+        port = s_.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(port, q))
+    p.start()
+    p.join(60)
+    if p.is_alive():
+        p.kill()
+        pytest.fail("rendezvous with a missing rank did not time out")
+    assert q.get(timeout=5).startswith("error")
+
+
+def _mismatch_worker(rank, world, port, q):
+    """Rank 1 builds its optimizer for a different parameter count: the in-place all-gather must fail loudly
+    (shape check on the host) rather than exchange ranges that do not tile the vector."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    try:
+        sh = _sharding()
+        n = 1000 if rank == 0 else 1200
+        opt = sh.ShardedAdamEMA(torch.zeros(n), lr=1e-3, update_fn=lambda *a: None)
+        sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(sizes, torch.tensor([opt.shard], dtype=torch.int64))
+        ok = len({int(s_) for s_ in sizes}) == 1
+        if rank == 0:
+            q.put("consistent" if ok else "mismatch detected")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mismatched_shard_sizes_are_detected_before_the_exchange():
+    with socket.socket() as s_:
+        s_.bind(("127.0.0.1", 0))
+        port = s_.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert all(not p.is_alive() for p in procs)
+    assert q.get(timeout=5) == "mismatch detected"
