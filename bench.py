@@ -520,7 +520,7 @@ def write_edm_config(folder, batch, train_steps):
     return ini
 
 
-def edm_train_images_per_s(binary, batch=256, steps=(20, 220)):
+def edm_train_images_per_s(binary, batch=256, steps=(50, 450)):
     """Images/s of the reference's own EDM trainer (edm/main_edm.c + diffusion/train.c + every host module,
     unmodified) with the given kernel backend linked in.  Config: channels 64/128/128, emb 128, 1 head, t 0.3,
     batch 256, Adam lr 1e-3, EMA 0.999, TF32 GEMMs, synthetic 28x28 images (pixel -1 with p=0.8, else U(-1,1)).
