@@ -73,6 +73,7 @@ SIGNATURES = {
     "b200_wn_forward_all": "s",
     "b200_wn_backward_flush": "s",
     "launch_axpby_rows": "pppppiis",
+    "launch_col2im_assign": "ppiiiiiiiiis",
     "launch_layernorm_backward_noalloc": "ppppppppiis",
     # management
     "b200_set_error_mode": "i",

@@ -12,7 +12,8 @@
  *     running im2col again (conv2d.c:46); it is recomputed only if forward has not run on
  *     that input since the buffer was last overwritten;
  *   - 1x1 / stride 1 / no padding convolutions are plain GEMMs on the activation itself:
- *     no im2col, no col2im, no memset.
+ *     no im2col, no col2im, no memset;
+ *   - col2im overwrites grad_in (launch_col2im_assign) instead of accumulating into a cleared buffer.
  *
  * Everything else (weight layout W[K*K*C_in, C_out], forced weight normalisation in place on
  * every forward, g_gain accumulated by launch_weight_normalize_backward after a memset,
@@ -20,6 +21,7 @@
  */
 #include "gemm.h" /* reference src/gemm.h: row-major cuBLAS helpers */
 #include "nn.h"
+#include "b200_layer_kernels.h" /* launch_col2im_assign */
 #include <math.h>
 #include <stdlib.h>
 
@@ -104,8 +106,8 @@ static void b200_conv2d_backward(Module* self, const float* in, const float* out
     }
     if (!st->pointwise) {
         st->col_src = NULL; /* the column buffer now holds gradients */
-        NN_CUDA_CHECK(cudaMemsetAsync(grad_in, 0, (size_t)batch * st->Hi * st->Wi * st->C_in * sizeof(float), ctx->stream));
-        launch_col2im(grad_in, st->col, batch, st->Hi, st->Wi, st->C_in, st->K, st->stride, st->pad, st->Ho, st->Wo,
+        /* overwrite variant: no memset of grad_in and no read-back (conv2d.c:61-65 clears, then accumulates) */
+        launch_col2im_assign(grad_in, st->col, batch, st->Hi, st->Wi, st->C_in, st->K, st->stride, st->pad, st->Ho, st->Wo,
             ctx->stream);
     }
 }

@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(float* __restrict__ 
 
 // float4, stride-1 fast path of the gather: one thread per (input pixel, channel pack), coordinates
 // decoded once in 32-bit arithmetic, the K*K candidate taps unrolled so that their loads overlap.
-template <int KT>
+template <int KT, bool ASSIGN>
 __global__ void __launch_bounds__(256) col2im_taps_kernel(float4* __restrict__ grad_im,
     const float4* __restrict__ grad_col, int H, int W, int Cv, int K, int pad, int Ho, int Wo, unsigned total)
 {
@@ -153,9 +153,13 @@ __global__ void __launch_bounds__(256) col2im_taps_kernel(float4* __restrict__ g
                 }
             }
         }
-        float4 old = grad_im[i];
-        old.x += acc.x; old.y += acc.y; old.z += acc.z; old.w += acc.w;
-        grad_im[i] = old;
+        if (ASSIGN) {
+            grad_im[i] = acc;
+        } else {
+            float4 old = grad_im[i];
+            old.x += acc.x; old.y += acc.y; old.z += acc.z; old.w += acc.w;
+            grad_im[i] = old;
+        }
     }
 }
 
@@ -412,6 +416,30 @@ void launch_im2col(float* col, const float* im, int batch, int H, int W, int C, 
     B200_CHECK_LAUNCH();
 }
 
+static bool col2im_fast(float* grad_im, const float* grad_col, int batch, int H, int W, int C, int K, int stride, int pad,
+    int H_out, int W_out, bool assign, cudaStream_t s)
+{
+    const long n = (long)batch * H * W * C;
+    if (!(C % 4 == 0 && stride == 1 && aligned16(grad_im) && aligned16(grad_col) && n / 4 < 4294967296L
+            && (long)batch * H_out * W_out * K * K * (C / 4) < 4294967296L && !tune_get("col2im_flat", 0)))
+        return false;
+    float4* gi4 = reinterpret_cast<float4*>(grad_im);
+    const float4* gc4 = reinterpret_cast<const float4*>(grad_col);
+    const int grid = flat_grid(n / 4);
+    const unsigned total = (unsigned)(n / 4);
+    if (K == 3 && assign)
+        col2im_taps_kernel<3, true><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+    else if (K == 3)
+        col2im_taps_kernel<3, false><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+    else if (assign)
+        col2im_taps_kernel<0, true><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+    else
+        col2im_taps_kernel<0, false><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+    count_launch();
+    B200_CHECK_LAUNCH();
+    return true;
+}
+
 void launch_col2im(float* grad_im, const float* grad_col, int batch, int H, int W, int C, int K, int stride,
     int pad, int H_out, int W_out, cudaStream_t s)
 {
@@ -420,17 +448,9 @@ void launch_col2im(float* grad_im, const float* grad_col, int batch, int H, int 
     const long n = (long)batch * H * W * C;
     if (n == 0)
         return;
-    if (C % 4 == 0 && stride == 1 && aligned16(grad_im) && aligned16(grad_col) && n / 4 < 4294967296L
-        && (long)batch * H_out * W_out * K * K * (C / 4) < 4294967296L && !tune_get("col2im_flat", 0)) {
-        float4* gi4 = reinterpret_cast<float4*>(grad_im);
-        const float4* gc4 = reinterpret_cast<const float4*>(grad_col);
-        if (K == 3)
-            col2im_taps_kernel<3><<<flat_grid(n / 4), 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out,
-                (unsigned)(n / 4));
-        else
-            col2im_taps_kernel<0><<<flat_grid(n / 4), 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out,
-                (unsigned)(n / 4));
-    } else if (C % 4 == 0 && aligned16(grad_im) && aligned16(grad_col))
+    if (col2im_fast(grad_im, grad_col, batch, H, W, C, K, stride, pad, H_out, W_out, false, s))
+        return;
+    if (C % 4 == 0 && aligned16(grad_im) && aligned16(grad_col))
         col2im_gather_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(grad_im, grad_col, H, W, C, K, stride, pad, H_out,
             W_out, n / 4);
     else
@@ -438,6 +458,21 @@ void launch_col2im(float* grad_im, const float* grad_col, int batch, int H, int 
             n);
     count_launch();
     B200_CHECK_LAUNCH();
+}
+
+void launch_col2im_assign(float* grad_im, const float* grad_col, int batch, int H, int W, int C, int K, int stride,
+    int pad, int H_out, int W_out, cudaStream_t s)
+{
+    B200_REQUIRE(batch >= 0 && H > 0 && W > 0 && C > 0 && K > 0 && stride > 0 && H_out > 0 && W_out > 0,
+        "col2im_assign: bad extents");
+    const long n = (long)batch * H * W * C;
+    if (n == 0)
+        return;
+    if (col2im_fast(grad_im, grad_col, batch, H, W, C, K, stride, pad, H_out, W_out, true, s))
+        return;
+    // shapes outside the fast path: clear, then accumulate as launch_col2im does
+    B200_CUDA_OK(cudaMemsetAsync(grad_im, 0, (size_t)n * sizeof(float), s));
+    launch_col2im(grad_im, grad_col, batch, H, W, C, K, stride, pad, H_out, W_out, s);
 }
 
 void launch_avg_pool_2x(float* out, const float* in, int batch, int H, int W, int C, cudaStream_t s)

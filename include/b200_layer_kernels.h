@@ -232,6 +232,11 @@ void b200_wn_batch_mode(int mode);
 int b200_wn_forward_all(cudaStream_t s);
 int b200_wn_backward_flush(cudaStream_t s);
 
+/* launch_col2im (nn.h, kernels.cu:800-838) that OVERWRITES grad_im instead of accumulating into it: saves the
+   cudaMemsetAsync of grad_im and its read-back that conv2d.c:61-65 pays before every col2im. */
+void launch_col2im_assign(float* grad_im, const float* grad_col, int batch, int H, int W, int C, int K,
+    int stride, int pad, int H_out, int W_out, cudaStream_t s);
+
 /* out[r,:] = wa[r]*a[r,:] + wb[r]*b[r,:] with per-row DEVICE coefficients: one
    launch for the per-sample launch_weighted_sum loops of diffusion/edm.c:56-64,
    :75-80, :205-207 and loss.c:65-70.  Aliasing as for launch_weighted_sum. */

@@ -64,6 +64,10 @@ def test_im2col_col2im(lib, orc, C, K, stride, pad):
     tg = torch.zeros(B, H, W, C, device="cuda")
     lib.launch_col2im(_p(tg), _p(_t(gcol)), B, H, W, C, K, stride, pad, Ho, Wo, _st())
     assert cases.rel_err(_n(tg), gim) <= 1e-6
+    # the overwriting variant gives the same result on a buffer full of garbage
+    ta = torch.full((B, H, W, C), 123.0, device="cuda")
+    lib.launch_col2im_assign(_p(ta), _p(_t(gcol)), B, H, W, C, K, stride, pad, Ho, Wo, _st())
+    assert torch.equal(ta, tg)
 
 
 @pytest.mark.parametrize("C", [8, 5])
