@@ -74,6 +74,9 @@ SIGNATURES = {
     "b200_wn_backward_flush": "s",
     "launch_axpby_rows": "pppppiis",
     "launch_col2im_assign": "ppiiiiiiiiis",
+    "launch_film_act_forward": "pppiiiiis",
+    "launch_film_act_backward": "pppppiiiiis",
+    "launch_activation_backward_axpy": "ppppfiis",
     "launch_layernorm_backward_noalloc": "ppppppppiis",
     # management
     "b200_set_error_mode": "i",

@@ -378,6 +378,102 @@ struct BroadcastOp {
     }
 };
 
+// out = act(in * (v[b, c] + 1)): FiLM modulation followed by the activation (cond_conv_residual.c:31-33)
+template <int ACT>
+struct FilmActOp {
+    float* out;
+    const float* in;
+    const float* v;
+    unsigned C, HWC;
+    template <int W> struct Regs { Pack<W> x, s; };
+    template <int W> __device__ void load(long e, Regs<W>& r) const
+    {
+        r.x = load_stream<W>(in + e);
+        const unsigned c = (unsigned)e % C, b = (unsigned)e / HWC;
+        r.s = load_cached<W>(v + (size_t)b * C + c);
+    }
+    template <int W> __device__ void store(long e, const Regs<W>& r) const
+    {
+        Pack<W> y;
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+            y.v[k] = act_value<ACT>(r.x.v[k] * (r.s.v[k] + 1.0f));
+        store_stream<W>(out + e, y);
+    }
+};
+
+// out = w * skip + gz * act'(z): activation backward joined with the skip branch of mp_sum's backward
+// (cond_conv_residual.c:54, :61)
+template <int ACT>
+struct ActBwdAxpyOp {
+    float* out;
+    const float* gz;
+    const float* z;
+    const float* skip;
+    float w;
+    template <int W> struct Regs { Pack<W> g, z, k; };
+    template <int W> __device__ void load(long e, Regs<W>& r) const
+    {
+        r.g = load_stream<W>(gz + e);
+        r.z = load_stream<W>(z + e);
+        r.k = load_stream<W>(skip + e);
+    }
+    template <int W> __device__ void store(long e, const Regs<W>& r) const
+    {
+        Pack<W> y;
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+            y.v[k] = fmaf(w, r.k.v[k], r.g.v[k] * act_slope<ACT>(r.z.v[k]));
+        store_stream<W>(out + e, y);
+    }
+};
+
+// FiLM + activation backward.  z = in*(cond+1); g = grad_out*act'(z); grad_in = g*(cond+1);
+// grad_cond[b,c] = sum_hw g*in.  block = 32 columns x 8 row lanes, grid = (ceil(C/32), batch, row splits);
+// with row splits > 1 the per-split sums go to `partial[split][b][c]` and a second tiny kernel adds them.
+template <int ACT>
+__global__ void __launch_bounds__(256) film_act_backward_kernel(float* __restrict__ grad_in, float* __restrict__ sums,
+    const float* __restrict__ grad_out, const float* __restrict__ in, const float* __restrict__ cond, int HW, int C,
+    int rows_per_split)
+{
+    __shared__ float part[8][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    const int b = blockIdx.y;
+    const int r_lo = blockIdx.z * rows_per_split, r_hi = min(HW, r_lo + rows_per_split);
+    float acc = 0.0f;
+    if (col < C) {
+        const float m = cond[(size_t)b * C + col] + 1.0f;
+        const size_t base = (size_t)b * HW * C + col;
+        for (int r = r_lo + threadIdx.y; r < r_hi; r += 8) {
+            const size_t k = base + (size_t)r * C;
+            const float x = in[k];
+            const float g = grad_out[k] * act_slope<ACT>(x * m);
+            acc = fmaf(g, x, acc);
+            grad_in[k] = g * m;
+        }
+    }
+    part[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < C) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            t += part[k][threadIdx.x];
+        sums[((size_t)blockIdx.z * gridDim.y + b) * C + col] = t;
+    }
+}
+
+__global__ void film_fold_splits_kernel(float* __restrict__ out, const float* __restrict__ partial, int n, int splits)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float t = 0.0f;
+        for (int s = 0; s < splits; ++s)
+            t += partial[(size_t)s * n + i];
+        out[i] = t;
+    }
+}
+
 // out[r,:] = wa[r]*a[r,:] + wb[r]*b[r,:]
 struct AxpbyRowsOp {
     float* out;
@@ -444,6 +540,37 @@ static void split_launch(float* ga, float* gb, const float* g, float wa, float w
     B200_REQUIRE(rows * ((long)Ca + Cb) < 2147483648L, "split: more than 2^31-1 elements");
     const bool vec = Ca % 4 == 0 && Cb % 4 == 0 && aligned16(ga) && aligned16(gb) && aligned16(g);
     ew_launch(SplitOp{ ga, gb, g, wa, wb, (unsigned)Ca, (unsigned)Cb }, rows * ((long)Ca + Cb), vec, s);
+}
+
+template <int ACT>
+static void film_act_backward_launch(float* grad_in, float* grad_cond, const float* grad_out, const float* in,
+    const float* cond, int batch, int HW, int C, cudaStream_t s)
+{
+    // enough CTAs to fill the GPU: split the rows of a sample when (C/32)*batch alone is too few
+    const int base_ctas = ((C + 31) / 32) * batch;
+    int splits = 1;
+    while (splits < 16 && base_ctas * splits < 4 * sm_count() && HW / (splits * 2) >= 64)
+        splits *= 2;
+    const int rows_per_split = (HW + splits - 1) / splits;
+    float* sums = grad_cond;
+    if (splits > 1) {
+        Scratch sc;
+        if (!scratch_get(s, (size_t)splits * batch * C, 0, &sc)) {
+            report_error(__FILE__, __LINE__, "film_act_backward: no scratch memory");
+            return;
+        }
+        sums = sc.partials;
+    }
+    film_act_backward_kernel<ACT><<<dim3((C + 31) / 32, batch, splits), dim3(32, 8), 0, s>>>(grad_in, sums, grad_out, in,
+        cond, HW, C, rows_per_split);
+    count_launch();
+    B200_CHECK_LAUNCH();
+    if (splits > 1) {
+        const int n = batch * C;
+        film_fold_splits_kernel<<<(n + 255) / 256, 256, 0, s>>>(grad_cond, sums, n, splits);
+        count_launch();
+        B200_CHECK_LAUNCH();
+    }
 }
 
 }  // namespace b200
@@ -587,6 +714,42 @@ void launch_spatial_modulate(float* out, const float* in, const float* cond, int
     B200_REQUIRE(batch >= 0 && H > 0 && W > 0 && C > 0 && n < 2147483648L, "spatial_modulate: bad extents");
     const bool vec = C % 4 == 0 && aligned16(out) && aligned16(in) && aligned16(cond);
     ew_launch(BroadcastOp<2>{ out, in, cond, (unsigned)C, (unsigned)(H * W * C) }, n, vec, s);
+}
+
+void launch_film_act_forward(float* out, const float* in, const float* cond, int batch, int H, int W, int C,
+    b200_act_t act, cudaStream_t s)
+{
+    const long n = (long)batch * H * W * C;
+    B200_REQUIRE(batch >= 0 && H > 0 && W > 0 && C > 0 && n < 2147483648L, "film_act_forward: bad extents");
+    const bool vec = C % 4 == 0 && aligned16(out) && aligned16(in) && aligned16(cond);
+    const bool ok = dispatch_act<FilmActOp>((int)act, n, vec, s, out, in, cond, (unsigned)C, (unsigned)(H * W * C));
+    B200_REQUIRE(ok, "film_act_forward: unknown activation %d", (int)act);
+}
+
+void launch_film_act_backward(float* grad_in, float* grad_cond, const float* grad_out, const float* in,
+    const float* cond, int batch, int H, int W, int C, b200_act_t act, cudaStream_t s)
+{
+    B200_REQUIRE(batch >= 0 && batch <= 65535 && H > 0 && W > 0 && C > 0, "film_act_backward: bad extents");
+    if (batch == 0)
+        return;
+    switch ((int)act) {
+    case ACT_IDENTITY: film_act_backward_launch<ACT_IDENTITY>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    case ACT_RELU: film_act_backward_launch<ACT_RELU>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    case ACT_GELU: film_act_backward_launch<ACT_GELU>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    case ACT_SILU: film_act_backward_launch<ACT_SILU>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    case ACT_TANH: film_act_backward_launch<ACT_TANH>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    case ACT_MP_SILU: film_act_backward_launch<ACT_MP_SILU>(grad_in, grad_cond, grad_out, in, cond, batch, H * W, C, s); break;
+    default: report_error(__FILE__, __LINE__, "film_act_backward: unknown activation %d", (int)act);
+    }
+}
+
+void launch_activation_backward_axpy(float* out, const float* grad_out, const float* in, const float* skip, float w_skip,
+    int n, b200_act_t act, cudaStream_t s)
+{
+    B200_REQUIRE(n >= 0, "activation_backward_axpy: n=%d", n);
+    const bool vec = aligned16(out) && aligned16(grad_out) && aligned16(in) && aligned16(skip);
+    const bool ok = dispatch_act<ActBwdAxpyOp>((int)act, n, vec, s, out, grad_out, in, skip, w_skip);
+    B200_REQUIRE(ok, "activation_backward_axpy: unknown activation %d", (int)act);
 }
 
 void launch_axpby_rows(float* out, const float* a, const float* b, const float* wa, const float* wb,

@@ -232,6 +232,20 @@ void b200_wn_batch_mode(int mode);
 int b200_wn_forward_all(cudaStream_t s);
 int b200_wn_backward_flush(cudaStream_t s);
 
+/* Fusions inside the EDM residual block (cond_conv_residual.c:24-63):
+   - out = act(in * (cond[b,c] + 1)): launch_spatial_modulate + launch_activation_forward in one pass; the
+     modulated tensor itself is not materialised.
+   - its backward: z = in*(cond+1), g = grad_out*act'(z), grad_in = g*(cond+1), grad_cond[b,c] = sum_hw g*in
+     (launch_activation_backward + launch_spatial_modulate_backward; z is recomputed, not read).
+   - out = w_skip*skip + grad_out*act'(in): launch_activation_backward + the skip branch of mp_sum's backward
+     (launch_weighted_sum with wb = 1). `out` may alias `grad_out`. */
+void launch_film_act_forward(float* out, const float* in, const float* cond, int batch, int H, int W, int C,
+    b200_act_t act, cudaStream_t s);
+void launch_film_act_backward(float* grad_in, float* grad_cond, const float* grad_out, const float* in,
+    const float* cond, int batch, int H, int W, int C, b200_act_t act, cudaStream_t s);
+void launch_activation_backward_axpy(float* out, const float* grad_out, const float* in, const float* skip,
+    float w_skip, int n, b200_act_t act, cudaStream_t s);
+
 /* launch_col2im (nn.h, kernels.cu:800-838) that OVERWRITES grad_im instead of accumulating into it: saves the
    cudaMemsetAsync of grad_im and its read-back that conv2d.c:61-65 pays before every col2im. */
 void launch_col2im_assign(float* grad_im, const float* grad_col, int batch, int H, int W, int C, int K,

@@ -241,3 +241,39 @@ def test_channel_cat_split_plain(lib, orc):
         lib.launch_channel_split(_p(ga), _p(gb), _p(_t(g)), rows, Ca, Cb, _st())
         ra, rb = orc.channel_split(g, Ca, Cb)
         assert np.array_equal(_n(ga), ra) and np.array_equal(_n(gb), rb)
+
+
+@pytest.mark.parametrize("B,H,W,C", [(3, 7, 7, 24), (2, 32, 32, 32), (5, 9, 4, 6), (64, 14, 14, 128)])
+@pytest.mark.parametrize("act", [5, 3, 0])
+def test_fused_residual_block_passes_match_their_compositions(lib, B, H, W, C, act):
+    """launch_film_act_forward / _backward and launch_activation_backward_axpy against the sequences of
+    reference launchers they replace (cond_conv_residual.c:31-33, :49-54, :54+:61)."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + C)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    h1, cond, gout, skip = rn(B, H, W, C), 0.3 * rn(B, C), rn(B, H, W, C), rn(B, H, W, C)
+    n = h1.numel()
+    # forward
+    h2, want = torch.empty_like(h1), torch.empty_like(h1)
+    lib.launch_spatial_modulate(_p(h2), _p(h1), _p(cond), B, H, W, C, _st())
+    lib.launch_activation_forward(_p(want), _p(h2), n, act, _st())
+    got = torch.empty_like(h1)
+    lib.launch_film_act_forward(_p(got), _p(h1), _p(cond), B, H, W, C, act, _st())
+    assert torch.equal(got, want)
+    # backward
+    gh2, gh1_want, gc_want = torch.empty_like(h1), torch.empty_like(h1), torch.empty(B, C, device="cuda")
+    lib.launch_activation_backward(_p(gh2), _p(gout), _p(h2), n, act, _st())
+    lib.launch_spatial_modulate_backward(_p(gh1_want), _p(gc_want), _p(gh2), _p(h1), _p(cond), B, H, W, C, _st())
+    gh1, gc = torch.empty_like(h1), torch.full((B, C), 7.0, device="cuda")
+    lib.launch_film_act_backward(_p(gh1), _p(gc), _p(gout), _p(h1), _p(cond), B, H, W, C, act, _st())
+    torch.cuda.synchronize()
+    assert cases.rel_err(_n(gh1), _n(gh1_want)) <= 1e-6
+    assert cases.rel_err(_n(gc), _n(gc_want)) <= 2e-5  # different summation order over H*W
+    # activation backward + skip
+    gx, want2 = torch.empty_like(h1), torch.empty_like(h1)
+    lib.launch_activation_backward(_p(gx), _p(gout), _p(h1), n, act, _st())
+    lib.launch_weighted_sum(_p(want2), _p(skip), _p(gx), F(0.8), F(1.0), n, _st())
+    got2 = torch.empty_like(h1)
+    lib.launch_activation_backward_axpy(_p(got2), _p(gout), _p(h1), _p(skip), F(0.8), n, act, _st())
+    torch.cuda.synchronize()
+    assert cases.rel_err(_n(got2), _n(want2)) <= 1e-6
