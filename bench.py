@@ -443,7 +443,7 @@ def ops_table(lib, fused, peak):
 
 
 # ------------------------------------------------------------------------------------ CPU baseline
-def cpu_baseline(threads=None, samples=16, min_seconds=8.0):
+def cpu_baseline(threads=None, samples=16, min_seconds=12.0):
     """The plain-C port (oracle/layer_oracle.c, fp32 accumulation) on the host cores over a bounded
     sample of the step: `samples` of the 256 images per GPU, same kernel sequence, repeated until
     about `min_seconds` of CPU time have been spent."""
@@ -472,7 +472,7 @@ def cpu_baseline(threads=None, samples=16, min_seconds=8.0):
         one()
         reps += 1
         dt = time.perf_counter() - t0
-        if dt >= min_seconds or reps >= 200:
+        if dt >= min_seconds or reps >= 5000:
             break
     nbytes = STEP_BYTES * samples / B * reps
     orc.set_accumulate_double(True)
