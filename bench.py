@@ -612,6 +612,7 @@ def main():
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--no-trainer", action="store_true", help="skip the EDM trainer legs (profiler captures)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
                     help="set a kernel tunable (b200_tune_set), e.g. gn_no_strip=1 to time the TMA tile kernels")
     ap.add_argument("--batch", type=int, default=256, help="samples per GPU; values other than 256 are for profiling only")
@@ -720,6 +721,7 @@ def main():
         # EDM UNet training, images/s: weak scaling (256 per GPU) and strong scaling (256 in total)
         if world > 1:
             torch.distributed.barrier()
+    if args.impl == "b200" and not args.no_ops and not args.no_trainer:
         dp = {"weak_256_per_gpu": edm_dp_train(world, rank, local, 256)}
         if world > 1:
             torch.distributed.barrier()
@@ -735,7 +737,7 @@ def main():
             torch.cuda.empty_cache()
             line["ops"] = ops_table(lib_run, fused, peak)
             exe = ROOT / "oracle" / "_ref" / ("edm_demo_b200" if args.impl == "b200" else "edm_demo_ref")
-            edm = edm_train_images_per_s(exe)
+            edm = None if args.no_trainer else edm_train_images_per_s(exe)
             if edm is not None:
                 line["edm_unet_train"] = edm
         print(json.dumps(line))
