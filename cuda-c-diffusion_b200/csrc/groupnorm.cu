@@ -1,26 +1,27 @@
 // NHWC GroupNorm forward / backward, optionally fused with an activation
 // (reference: src/kernels.cu:622-745, composed with :103-117 by conv_residual.c).
 //
-// Tile kernels (the fast path).  x is viewed as a matrix [B*HW, C].  A work item
-// is (sample b, channel tile of Ct channels covering whole groups); a
-// thread-block cluster of CS CTAs splits the HW rows of the item, so the cluster
-// together holds every element of Ct/cpg groups of one sample in shared memory:
-//   * x (and dy) cross HBM exactly once: bulk tensor copies (TMA) bring a tile
-//     in, statistics and the result are both produced from shared memory, and
-//     the result leaves through TMA stores;
-//   * clusters are persistent and double-buffered: while item i is being
-//     reduced / normalised / stored, the loads of item i+1 are already in flight
-//     into the other buffer, so each SM keeps HBM requests outstanding through
-//     the synchronisation-heavy phases;
-//   * per-channel partial statistics are folded with warp shuffles, then across
-//     the cluster through distributed shared memory (no global round trip);
-//   * backward reuses the per-channel sums of dy and dy*xhat for BOTH the group
-//     sums that dx needs and the per-sample dgamma/dbeta partials; the last
-//     item of a channel tile (atomic ticket) adds the partials in a fixed order,
-//     so parameter gradients are overwritten and bit-reproducible.
-// Shapes the tile path cannot take (C % 4 != 0, no usable row chunking, a
-// sample tile larger than a cluster's shared memory, misaligned pointers) use
-// the generic kernels further down.
+// x is viewed as a matrix [B*HW, C]; a work item is (sample b, Ct channels covering whole groups).
+// Four kernel families, tried in this order by gn_forward / gn_backward:
+//
+//   1. register-resident strips (groupnorm_strip.cuh): the default.  A CTA keeps all HW rows of an
+//      item in registers, statistics and output come from registers, the next item is staged with
+//      cp.async while the current one is processed.  x (and dy) cross HBM exactly once.
+//   2. chunked strips (groupnorm_cstrip.cuh): samples too tall for the register file; the strip is
+//      walked twice in chunks, the second read coming from L2 while the strips in flight fit there.
+//   3. tile kernels (this file), kept selectable (tunables gn_no_strip / gn_no_cstrip): a thread-block
+//      cluster of CS CTAs splits the rows of an item and holds it in shared memory; 2-D bulk tensor
+//      copies (TMA) with mbarrier completion bring tiles in and take results out, clusters are
+//      persistent and double-buffered, per-channel partial statistics are folded with warp shuffles
+//      and across the cluster through distributed shared memory, and the last item of a channel tile
+//      (atomic ticket) adds the per-sample dgamma/dbeta partials in a fixed order.  Every wait on an
+//      mbarrier is bounded and reports through the device error word.  Slower than 1 and 2 on every
+//      shape measured (the cluster barrier and the DSMEM round trip sit on each item's critical path).
+//   4. generic kernels (this file): any shape, any alignment (C % 4 != 0, misaligned pointers).
+//
+// Backward in every family reuses the per-channel sums of g and g*xhat (g = dy * act'(z)) for BOTH
+// the group sums that dx needs and the per-sample dgamma/dbeta partials, which a fixed-order fold
+// adds up: parameter gradients are overwritten and bit-reproducible.
 #include "dev_common.cuh"
 #include "tma_desc.cuh"
 #include "../../include/b200_layer_kernels.h"
