@@ -5,9 +5,12 @@
 // (reference: src/kernels.cu:119-161, :750-1178, :1284-1313).
 //
 // These sit either side of the fused layer kernels in a training step.  They
-// are written as straightforward coalesced sm_100a kernels: channel-contiguous
-// float4 accesses where C % 4 == 0, gathers instead of atomic scatters
-// (col2im), and strip reductions instead of one serial thread per output.
+// are coalesced sm_100a kernels: channel-contiguous float4 accesses where
+// C % 4 == 0, gathers instead of atomic scatters (col2im), strip reductions
+// instead of one serial thread per output.  im2col / col2im, which move nine
+// times the activation per 3x3 convolution, decode their coordinates once per
+// (pixel, channel pack) and walk the K*K taps with all loads in flight; an
+// overwriting col2im saves the caller's memset and read-back.
 #include "dev_common.cuh"
 #include "../../include/b200_layer_kernels.h"
 

@@ -9,7 +9,9 @@
 // (single read of W), column sums of squares are folded in shared memory and
 // then across the cluster through distributed shared memory, and the scaled
 // values are written straight from registers.  A table of matrices lets one
-// launch normalise every MP weight of a model.
+// launch normalise every MP weight of a model, forward and backward; hosts whose
+// modules call the per-weight launchers can have those calls recorded once and
+// then batched (b200_wn_batch_mode).
 // Shapes outside the cluster kernel's limits (out % 4 != 0, in > 2048,
 // misaligned) use the strip kernel (two sweeps, any shape).
 #include "dev_common.cuh"
