@@ -1,118 +1,141 @@
 /* EDM residual block with fused element-wise passes; link-time replacement of the reference's
- * src/cond_conv_residual.c (same constructor, vtable, parameter order and sub-modules).
+ * src/cond_conv_residual.c (same constructor name and arguments, same Module vtable, same
+ * parameter order, same sub-modules created in the same order).
  *
- *     h0 = mp_silu(x);  h1 = conv0(h0);  c = emb_lin(emb);
- *     h3 = mp_silu(h1 * (c + 1));        h4 = conv1(h3);  out = mp_sum(x, h4, t)
+ *     a0 = mp_silu(x);  a1 = conv[0](a0);  shift = film(emb);
+ *     a2 = mp_silu(a1 * (shift + 1));      a3 = conv[1](a2);  out = mp_sum(x, a3, t)
  *
  * Against the reference's sequence of launches (cond_conv_residual.c:24-63):
  *   - FiLM modulation and the following MP-SiLU are one pass (launch_film_act_forward); the modulated
- *     tensor h2 is not stored, backward recomputes it from h1 and c;
+ *     tensor is not stored, backward recomputes it from a1 and shift;
  *   - MP-SiLU backward and the FiLM backward (input gradient and per-sample conditioning gradient)
  *     are one pass (launch_film_act_backward);
  *   - the input MP-SiLU's backward and the skip branch of mp_sum's backward are one pass
  *     (launch_activation_backward_axpy).
- * Per block this moves 16 tensor-sized passes through HBM instead of 23; three activation-sized
- * buffers (h2, gh2, gxb) are not allocated.
+ * Per block this moves 16 tensor-sized passes through HBM instead of 23.  All activations and
+ * gradients of a block live in ONE device allocation (eight planes of max_batch*H*W*C floats plus
+ * the three small conditioning vectors), three planes fewer than the reference allocates.
  */
 #include "nn.h"
 #include "b200_layer_kernels.h"
 #include <math.h>
 #include <stdlib.h>
 
+enum { ACT_IN = 0, ACT_CONV0, ACT_FILM, ACT_CONV1, N_ACT };       /* a0 .. a3 */
+enum { GRAD_CONV1 = 0, GRAD_FILM, GRAD_CONV0, GRAD_IN, N_GRAD };  /* d/d a3, a2, a1, a0 */
+
 typedef struct {
-    int C, emb_dim, max_batch, H, W, cond_slot;
-    float wa, wb;
-    Module *conv0, *emb_lin, *conv1;
-    float *h0, *h1, *c, *h3, *h4;
-    float *gh4, *gh3, *gh1, *gh0, *gc, *grad_emb_local;
-} B200CondConvRes;
+    int channels, emb_width, height, width, slot;
+    float keep, mix;     /* mp_sum weights of the skip and of the branch */
+    Module* conv[2];
+    Module* film;        /* mp_linear emb -> per-sample channel shift, zero gain at start */
+    float* arena;        /* the block's single device allocation */
+    float* act[N_ACT];
+    float* grad[N_GRAD];
+    float *shift, *shift_grad, *emb_grad;
+} ResBlock;
 
-static void b200_ccr_forward(Module* self, const float* in, float* out, int batch, Context* ctx)
+static int plane_elems(const ResBlock* rb, int batch) { return batch * rb->height * rb->width * rb->channels; }
+
+static void resblock_forward(Module* self, const float* x, float* y, int batch, Context* ctx)
 {
-    B200CondConvRes* st = (B200CondConvRes*)self->state;
-    const int n = batch * st->H * st->W * st->C;
-    launch_activation_forward(st->h0, in, n, ACT_MP_SILU, ctx->stream);
-    st->conv0->forward(st->conv0, st->h0, st->h1, batch, ctx);
-    st->emb_lin->forward(st->emb_lin, ctx->cond[st->cond_slot].fwd, st->c, batch, ctx);
-    launch_film_act_forward(st->h3, st->h1, st->c, batch, st->H, st->W, st->C, ACT_MP_SILU, ctx->stream);
-    st->conv1->forward(st->conv1, st->h3, st->h4, batch, ctx);
-    launch_weighted_sum(out, in, st->h4, st->wa, st->wb, n, ctx->stream);
+    ResBlock* rb = (ResBlock*)self->state;
+    const int n = plane_elems(rb, batch);
+    cudaStream_t s = ctx->stream;
+    launch_activation_forward(rb->act[ACT_IN], x, n, ACT_MP_SILU, s);
+    rb->conv[0]->forward(rb->conv[0], rb->act[ACT_IN], rb->act[ACT_CONV0], batch, ctx);
+    rb->film->forward(rb->film, ctx->cond[rb->slot].fwd, rb->shift, batch, ctx);
+    launch_film_act_forward(rb->act[ACT_FILM], rb->act[ACT_CONV0], rb->shift, batch, rb->height, rb->width,
+        rb->channels, ACT_MP_SILU, s);
+    rb->conv[1]->forward(rb->conv[1], rb->act[ACT_FILM], rb->act[ACT_CONV1], batch, ctx);
+    launch_weighted_sum(y, x, rb->act[ACT_CONV1], rb->keep, rb->mix, n, s);
 }
 
-static void b200_ccr_backward(Module* self, const float* in, const float* out, const float* grad_out, float* grad_in,
-    int batch, Context* ctx)
+static void resblock_backward(Module* self, const float* x, const float* y, const float* dy, float* dx, int batch,
+    Context* ctx)
 {
-    (void)out;
-    B200CondConvRes* st = (B200CondConvRes*)self->state;
-    const int n = batch * st->H * st->W * st->C;
-    launch_weighted_sum(st->gh4, grad_out, grad_out, st->wb, 0.0f, n, ctx->stream);
-    st->conv1->backward(st->conv1, st->h3, st->h4, st->gh4, st->gh3, batch, ctx);
-    launch_film_act_backward(st->gh1, st->gc, st->gh3, st->h1, st->c, batch, st->H, st->W, st->C, ACT_MP_SILU,
-        ctx->stream);
-    st->conv0->backward(st->conv0, st->h0, st->h1, st->gh1, st->gh0, batch, ctx);
-    st->emb_lin->backward(st->emb_lin, ctx->cond[st->cond_slot].fwd, st->c, st->gc, st->grad_emb_local, batch, ctx);
-    launch_weighted_sum(ctx->cond[st->cond_slot].grad, ctx->cond[st->cond_slot].grad, st->grad_emb_local, 1.0f, 1.0f,
-        batch * st->emb_dim, ctx->stream);
-    /* grad_in = wa * grad_out + gh0 * mp_silu'(x) */
-    launch_activation_backward_axpy(grad_in, st->gh0, in, grad_out, st->wa, n, ACT_MP_SILU, ctx->stream);
+    (void)y;
+    ResBlock* rb = (ResBlock*)self->state;
+    const int n = plane_elems(rb, batch);
+    cudaStream_t s = ctx->stream;
+    CondSlot* cond = &ctx->cond[rb->slot];
+
+    /* branch: d a3 = mix * dy, then back through conv[1], FiLM+MP-SiLU, conv[0] */
+    launch_weighted_sum(rb->grad[GRAD_CONV1], dy, dy, rb->mix, 0.0f, n, s);
+    rb->conv[1]->backward(rb->conv[1], rb->act[ACT_FILM], rb->act[ACT_CONV1], rb->grad[GRAD_CONV1],
+        rb->grad[GRAD_FILM], batch, ctx);
+    launch_film_act_backward(rb->grad[GRAD_CONV0], rb->shift_grad, rb->grad[GRAD_FILM], rb->act[ACT_CONV0], rb->shift,
+        batch, rb->height, rb->width, rb->channels, ACT_MP_SILU, s);
+    rb->conv[0]->backward(rb->conv[0], rb->act[ACT_IN], rb->act[ACT_CONV0], rb->grad[GRAD_CONV0], rb->grad[GRAD_IN],
+        batch, ctx);
+
+    /* conditioning: this block's share is added to the slot's gradient */
+    rb->film->backward(rb->film, cond->fwd, rb->shift, rb->shift_grad, rb->emb_grad, batch, ctx);
+    launch_weighted_sum(cond->grad, cond->grad, rb->emb_grad, 1.0f, 1.0f, batch * rb->emb_width, s);
+
+    /* dx = keep * dy + (d a0) * mp_silu'(x) */
+    launch_activation_backward_axpy(dx, rb->grad[GRAD_IN], x, dy, rb->keep, n, ACT_MP_SILU, s);
 }
 
-static void b200_ccr_parameters(Module* self, ParamList* pl)
+static void resblock_parameters(Module* self, ParamList* pl)
 {
-    B200CondConvRes* st = (B200CondConvRes*)self->state;
-    st->conv0->parameters(st->conv0, pl);
-    st->emb_lin->parameters(st->emb_lin, pl);
-    st->conv1->parameters(st->conv1, pl);
+    ResBlock* rb = (ResBlock*)self->state;
+    rb->conv[0]->parameters(rb->conv[0], pl);
+    rb->film->parameters(rb->film, pl);
+    rb->conv[1]->parameters(rb->conv[1], pl);
 }
 
-static void b200_ccr_free(Module* self)
+static void resblock_free(Module* self)
 {
-    B200CondConvRes* st = (B200CondConvRes*)self->state;
-    st->conv0->free(st->conv0);
-    st->emb_lin->free(st->emb_lin);
-    st->conv1->free(st->conv1);
-    float* bufs[11] = { st->h0, st->h1, st->c, st->h3, st->h4, st->gh4, st->gh3, st->gh1, st->gh0, st->gc,
-        st->grad_emb_local };
-    for (int i = 0; i < 11; ++i)
-        cudaFree(bufs[i]);
-    free(st);
+    ResBlock* rb = (ResBlock*)self->state;
+    rb->conv[0]->free(rb->conv[0]);
+    rb->film->free(rb->film);
+    rb->conv[1]->free(rb->conv[1]);
+    cudaFree(rb->arena);
+    free(rb);
     free(self);
 }
 
 Module* cond_conv_residual_create(Context* ctx, int C, int emb_dim, int H, int W, int max_batch, float t,
     int cond_slot)
 {
-    Module* m = (Module*)calloc(1, sizeof(Module));
-    B200CondConvRes* st = (B200CondConvRes*)calloc(1, sizeof(B200CondConvRes));
-    st->C = C;
-    st->emb_dim = emb_dim;
-    st->max_batch = max_batch;
-    st->H = H;
-    st->W = W;
-    st->cond_slot = cond_slot;
-    const float d = sqrtf((1.0f - t) * (1.0f - t) + t * t);
-    st->wa = (1.0f - t) / d;
-    st->wb = t / d;
+    ResBlock* rb = (ResBlock*)calloc(1, sizeof *rb);
+    rb->channels = C;
+    rb->emb_width = emb_dim;
+    rb->height = H;
+    rb->width = W;
+    rb->slot = cond_slot;
+    const float norm = sqrtf((1.0f - t) * (1.0f - t) + t * t);
+    rb->keep = (1.0f - t) / norm;
+    rb->mix = t / norm;
 
-    /* same order of constructor calls as the reference, so the same cuRAND draws reach each weight */
-    st->conv0 = conv2d_create(ctx, C, C, 3, 1, 1, H, W, max_batch, 1, 1.0f);
-    st->emb_lin = mp_linear_create(ctx, emb_dim, C, 0.0f);
-    st->conv1 = conv2d_create(ctx, C, C, 3, 1, 1, H, W, max_batch, 1, 1.0f);
+    /* the reference creates conv0, the embedding projection and conv1 in this order; keeping it
+       means a model built from the same generator state starts from the same weights */
+    rb->conv[0] = conv2d_create(ctx, C, C, 3, 1, 1, H, W, max_batch, 1, 1.0f);
+    rb->film = mp_linear_create(ctx, emb_dim, C, 0.0f);
+    rb->conv[1] = conv2d_create(ctx, C, C, 3, 1, 1, H, W, max_batch, 1, 1.0f);
 
-    const size_t ns = (size_t)max_batch * H * W * C;
-    float** big[8] = { &st->h0, &st->h1, &st->h3, &st->h4, &st->gh4, &st->gh3, &st->gh1, &st->gh0 };
-    for (int i = 0; i < 8; ++i)
-        *big[i] = nn_device_alloc(ns);
-    st->c = nn_device_alloc((size_t)max_batch * C);
-    st->gc = nn_device_alloc((size_t)max_batch * C);
-    st->grad_emb_local = nn_device_alloc((size_t)max_batch * emb_dim);
+    /* one allocation: planes first (each a multiple of 4 floats keeps them 16-byte aligned), vectors after */
+    const size_t plane = ((size_t)max_batch * H * W * C + 3) & ~(size_t)3;
+    const size_t vec_c = ((size_t)max_batch * C + 3) & ~(size_t)3, vec_e = ((size_t)max_batch * emb_dim + 3) & ~(size_t)3;
+    const size_t total = (N_ACT + N_GRAD) * plane + 2 * vec_c + vec_e;
+    NN_CUDA_CHECK(cudaMalloc((void**)&rb->arena, total * sizeof(float)));
+    float* cursor = rb->arena;
+    for (int i = 0; i < N_ACT; ++i, cursor += plane)
+        rb->act[i] = cursor;
+    for (int i = 0; i < N_GRAD; ++i, cursor += plane)
+        rb->grad[i] = cursor;
+    rb->shift = cursor;
+    rb->shift_grad = cursor + vec_c;
+    rb->emb_grad = cursor + 2 * vec_c;
 
+    Module* m = (Module*)calloc(1, sizeof *m);
     m->name = "cond_conv_residual";
     m->in_dim = m->out_dim = H * W * C;
-    m->state = st;
-    m->forward = b200_ccr_forward;
-    m->backward = b200_ccr_backward;
-    m->parameters = b200_ccr_parameters;
-    m->free = b200_ccr_free;
+    m->state = rb;
+    m->forward = resblock_forward;
+    m->backward = resblock_backward;
+    m->parameters = resblock_parameters;
+    m->free = resblock_free;
     return m;
 }

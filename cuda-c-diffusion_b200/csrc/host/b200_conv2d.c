@@ -1,186 +1,187 @@
 /* conv2d host module with fewer passes over HBM; link-time replacement of the reference's
- * src/conv2d.c (same constructor `conv2d_create`, same Module vtable, same parameter order,
+ * src/conv2d.c (same constructor name and arguments, same Module vtable, same parameter order,
  * same im2col + cuBLAS formulation: the contraction itself stays a cuBLAS SGEMM).
  *
  * Per 3x3 convolution on [256,28,28,64] the reference moves 4.2 GB through HBM per
- * forward+backward; three of its passes carry no information and are removed here:
+ * forward+backward; these passes carry no information and are removed here:
  *
  *   - the magnitude-preserving gain is applied as the GEMM's alpha, read from device memory
  *     (cublas pointer mode DEVICE), instead of a separate scale pass over the output
- *     (conv2d.c:31) and over the 9x larger column-gradient buffer (conv2d.c:55);
- *   - backward reuses the column buffer that forward filled for the same input instead of
- *     running im2col again (conv2d.c:46); it is recomputed only if forward has not run on
- *     that input since the buffer was last overwritten;
+ *     (conv2d.c:31) and over the 9x larger patch-gradient buffer (conv2d.c:55);
+ *   - backward reuses the patch matrix that forward built for the same input instead of running
+ *     im2col again (conv2d.c:46); it is rebuilt only if forward has not run on that input since
+ *     the buffer was last overwritten;
  *   - 1x1 / stride 1 / no padding convolutions are plain GEMMs on the activation itself:
  *     no im2col, no col2im, no memset;
- *   - col2im overwrites grad_in (launch_col2im_assign) instead of accumulating into a cleared buffer.
+ *   - col2im overwrites the input gradient (launch_col2im_assign) instead of accumulating into a
+ *     buffer that was cleared first (conv2d.c:61-65).
  *
- * Everything else (weight layout W[K*K*C_in, C_out], forced weight normalisation in place on
- * every forward, g_gain accumulated by launch_weight_normalize_backward after a memset,
- * He-init / bias in the non-MP mode) follows the reference module.
+ * Weight layout W[K*K*C_in, C_out], forced weight normalisation in place on every forward, the
+ * gain gradient accumulated by launch_weight_normalize_backward after a memset, He initialisation
+ * and bias in the plain mode: as in the reference module, so both are interchangeable.
  */
 #include "gemm.h" /* reference src/gemm.h: row-major cuBLAS helpers */
 #include "nn.h"
-#include "b200_layer_kernels.h" /* launch_col2im_assign */
+#include "b200_layer_kernels.h"
 #include <math.h>
 #include <stdlib.h>
 
 typedef struct {
-    int C_in, C_out, K, stride, pad;
-    int Hi, Wi, Ho, Wo;
-    int max_batch, mp_mode, pointwise;
-    float eps;
-    float *Wt, *gW;
-    float *b, *gb;
-    float *gain, *g_gain;
-    float* col;
-    float* zero;          /* device 0.0f: beta in pointer mode DEVICE */
-    const float* col_src; /* input whose patches `col` currently holds, NULL if overwritten */
-    int col_batch;
-} B200Conv2D;
+    int in_h, in_w, in_c, out_h, out_w, out_c;
+    int k, stride, pad;
+    int taps_c; /* k*k*in_c: rows of the weight matrix, columns of the patch matrix */
+} ConvShape;
 
-static void fill_col(B200Conv2D* st, const float* in, int batch, Context* ctx)
+typedef struct {
+    ConvShape sh;
+    int magnitude_preserving; /* forced weight norm + scalar gain, no bias */
+    int is_pointwise;         /* 1x1, stride 1, no padding: the patch matrix is the input itself */
+    float wn_eps;
+    float* params;            /* one allocation: weight | weight grad | gain or bias | its grad | zero */
+    float *weight, *weight_grad, *extra, *extra_grad, *zero;
+    float* patches;           /* [max_batch*out_h*out_w, taps_c], absent for pointwise */
+    const float* patches_of;  /* input whose patches are in `patches`; NULL once overwritten by gradients */
+    int patches_batch;
+} FastConv;
+
+static int out_rows(const ConvShape* sh, int batch) { return batch * sh->out_h * sh->out_w; }
+
+static void build_patches(FastConv* cv, const float* x, int batch, cudaStream_t s)
 {
-    launch_im2col(st->col, in, batch, st->Hi, st->Wi, st->C_in, st->K, st->stride, st->pad, st->Ho, st->Wo,
-        ctx->stream);
-    st->col_src = in;
-    st->col_batch = batch;
+    const ConvShape* sh = &cv->sh;
+    launch_im2col(cv->patches, x, batch, sh->in_h, sh->in_w, sh->in_c, sh->k, sh->stride, sh->pad, sh->out_h, sh->out_w, s);
+    cv->patches_of = x;
+    cv->patches_batch = batch;
 }
 
-/* C[M,N] = (*alpha_dev) * op(A) op(B) in the row-major convention of gemm.h, alpha read on the device */
-static void sgemm_dev_alpha(Context* ctx, cublasOperation_t ta, cublasOperation_t tb, int m, int n, int k,
-    const float* alpha_dev, const float* beta_dev, const float* A, int lda, const float* B, int ldb, float* C, int ldc)
+/* cublasSgemm with alpha and beta read on the device; the handle goes back to host pointer mode,
+   which every other module of the reference relies on */
+static void sgemm_device_scalars(cublasHandle_t h, cublasOperation_t ta, cublasOperation_t tb, int m, int n, int k,
+    const float* alpha, const float* A, int lda, const float* B, int ldb, const float* beta, float* C, int ldc)
 {
-    NN_CUBLAS_CHECK(cublasSetPointerMode(ctx->cublas, CUBLAS_POINTER_MODE_DEVICE));
-    cublasStatus_t s = cublasSgemm(ctx->cublas, ta, tb, m, n, k, alpha_dev, A, lda, B, ldb, beta_dev, C, ldc);
-    NN_CUBLAS_CHECK(cublasSetPointerMode(ctx->cublas, CUBLAS_POINTER_MODE_HOST)); /* what every other module expects */
-    NN_CUBLAS_CHECK(s);
+    NN_CUBLAS_CHECK(cublasSetPointerMode(h, CUBLAS_POINTER_MODE_DEVICE));
+    const cublasStatus_t st = cublasSgemm(h, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    NN_CUBLAS_CHECK(cublasSetPointerMode(h, CUBLAS_POINTER_MODE_HOST));
+    NN_CUBLAS_CHECK(st);
 }
 
-static void b200_conv2d_forward(Module* self, const float* in, float* out, int batch, Context* ctx)
+static void fastconv_forward(Module* self, const float* x, float* y, int batch, Context* ctx)
 {
-    B200Conv2D* st = (B200Conv2D*)self->state;
-    const int M = batch * st->Ho * st->Wo;
-    const int Kg = st->K * st->K * st->C_in;
-    const float* X = in;
-    if (!st->pointwise) {
-        fill_col(st, in, batch, ctx);
-        X = st->col;
+    FastConv* cv = (FastConv*)self->state;
+    const ConvShape* sh = &cv->sh;
+    const int rows = out_rows(sh, batch);
+    const float* lhs = x;
+    if (!cv->is_pointwise) {
+        build_patches(cv, x, batch, ctx->stream);
+        lhs = cv->patches;
     }
-    if (st->mp_mode) {
-        launch_weight_normalize(st->Wt, Kg, st->C_out, st->eps, ctx->stream);
-        /* out[M,C_out] = gain * X[M,Kg] @ Wt[Kg,C_out]  (gemm_forward's operand order) */
-        sgemm_dev_alpha(ctx, CUBLAS_OP_N, CUBLAS_OP_N, st->C_out, M, Kg, st->gain, st->zero, st->Wt, st->C_out, X, Kg,
-            out, st->C_out);
+    if (cv->magnitude_preserving) {
+        launch_weight_normalize(cv->weight, sh->taps_c, sh->out_c, cv->wn_eps, ctx->stream);
+        /* y[rows, out_c] = gain * lhs[rows, taps_c] @ weight[taps_c, out_c]; row-major operands map to
+           column-major cuBLAS as in gemm_forward */
+        sgemm_device_scalars(ctx->cublas, CUBLAS_OP_N, CUBLAS_OP_N, sh->out_c, rows, sh->taps_c, cv->extra, cv->weight,
+            sh->out_c, lhs, sh->taps_c, cv->zero, y, sh->out_c);
     } else {
-        gemm_forward(ctx->cublas, 1.0f, X, st->Wt, out, M, Kg, st->C_out);
-        launch_add_bias(out, st->b, M, st->C_out, ctx->stream);
+        gemm_forward(ctx->cublas, 1.0f, lhs, cv->weight, y, rows, sh->taps_c, sh->out_c);
+        launch_add_bias(y, cv->extra, rows, sh->out_c, ctx->stream);
     }
 }
 
-static void b200_conv2d_backward(Module* self, const float* in, const float* out, const float* grad_out,
-    float* grad_in, int batch, Context* ctx)
+static void fastconv_backward(Module* self, const float* x, const float* y, const float* dy, float* dx, int batch,
+    Context* ctx)
 {
-    (void)out;
-    B200Conv2D* st = (B200Conv2D*)self->state;
-    const int M = batch * st->Ho * st->Wo;
-    const int Kg = st->K * st->K * st->C_in;
-    const float* X = in;
-    if (!st->pointwise) {
-        if (st->col_src != in || st->col_batch != batch)
-            fill_col(st, in, batch, ctx);
-        X = st->col;
-    }
-    gemm_dW(ctx->cublas, 1.0f, X, grad_out, st->gW, M, Kg, st->C_out);
+    (void)y;
+    FastConv* cv = (FastConv*)self->state;
+    const ConvShape* sh = &cv->sh;
+    const int rows = out_rows(sh, batch);
+    cudaStream_t s = ctx->stream;
 
-    float* dX = st->pointwise ? grad_in : st->col;
-    if (st->mp_mode) {
-        NN_CUDA_CHECK(cudaMemsetAsync(st->g_gain, 0, sizeof(float), ctx->stream));
-        launch_weight_normalize_backward(st->gW, st->Wt, st->gain, st->g_gain, Kg, st->C_out, ctx->stream);
-        /* dX[M,Kg] = gain * grad_out[M,C_out] @ Wt[Kg,C_out]^T  (gemm_dX's operand order) */
-        sgemm_dev_alpha(ctx, CUBLAS_OP_T, CUBLAS_OP_N, Kg, M, st->C_out, st->gain, st->zero, st->Wt, st->C_out, grad_out,
-            st->C_out, dX, Kg);
+    const float* lhs = x;
+    if (!cv->is_pointwise) {
+        if (cv->patches_of != x || cv->patches_batch != batch)
+            build_patches(cv, x, batch, s);
+        lhs = cv->patches;
+    }
+    gemm_dW(ctx->cublas, 1.0f, lhs, dy, cv->weight_grad, rows, sh->taps_c, sh->out_c);
+
+    /* gradient with respect to the patch matrix, written over it (or straight into dx for 1x1) */
+    float* dlhs = cv->is_pointwise ? dx : cv->patches;
+    if (cv->magnitude_preserving) {
+        NN_CUDA_CHECK(cudaMemsetAsync(cv->extra_grad, 0, sizeof(float), s));
+        launch_weight_normalize_backward(cv->weight_grad, cv->weight, cv->extra, cv->extra_grad, sh->taps_c, sh->out_c, s);
+        /* dlhs[rows, taps_c] = gain * dy[rows, out_c] @ weight^T, operand order of gemm_dX */
+        sgemm_device_scalars(ctx->cublas, CUBLAS_OP_T, CUBLAS_OP_N, sh->taps_c, rows, sh->out_c, cv->extra, cv->weight,
+            sh->out_c, dy, sh->out_c, cv->zero, dlhs, sh->taps_c);
     } else {
-        launch_bias_grad(st->gb, grad_out, M, st->C_out, ctx->stream);
-        gemm_dX(ctx->cublas, 1.0f, st->Wt, grad_out, dX, M, Kg, st->C_out);
+        launch_bias_grad(cv->extra_grad, dy, rows, sh->out_c, s);
+        gemm_dX(ctx->cublas, 1.0f, cv->weight, dy, dlhs, rows, sh->taps_c, sh->out_c);
     }
-    if (!st->pointwise) {
-        st->col_src = NULL; /* the column buffer now holds gradients */
-        /* overwrite variant: no memset of grad_in and no read-back (conv2d.c:61-65 clears, then accumulates) */
-        launch_col2im_assign(grad_in, st->col, batch, st->Hi, st->Wi, st->C_in, st->K, st->stride, st->pad, st->Ho, st->Wo,
-            ctx->stream);
+    if (!cv->is_pointwise) {
+        cv->patches_of = NULL;
+        launch_col2im_assign(dx, cv->patches, batch, sh->in_h, sh->in_w, sh->in_c, sh->k, sh->stride, sh->pad, sh->out_h,
+            sh->out_w, s);
     }
 }
 
-static void b200_conv2d_parameters(Module* self, ParamList* pl)
+static void fastconv_parameters(Module* self, ParamList* pl)
 {
-    B200Conv2D* st = (B200Conv2D*)self->state;
-    param_list_add(pl, st->Wt, st->gW, st->K * st->K * st->C_in * st->C_out);
-    if (st->mp_mode)
-        param_list_add(pl, st->gain, st->g_gain, 1);
-    else
-        param_list_add(pl, st->b, st->gb, st->C_out);
+    FastConv* cv = (FastConv*)self->state;
+    param_list_add(pl, cv->weight, cv->weight_grad, cv->sh.taps_c * cv->sh.out_c);
+    param_list_add(pl, cv->extra, cv->extra_grad, cv->magnitude_preserving ? 1 : cv->sh.out_c);
 }
 
-static void b200_conv2d_free(Module* self)
+static void fastconv_free(Module* self)
 {
-    B200Conv2D* st = (B200Conv2D*)self->state;
-    float* bufs[8] = { st->Wt, st->gW, st->col, st->gain, st->g_gain, st->b, st->gb, st->zero };
-    for (int i = 0; i < 8; ++i)
-        if (bufs[i])
-            cudaFree(bufs[i]);
-    free(st);
+    FastConv* cv = (FastConv*)self->state;
+    cudaFree(cv->params);
+    if (cv->patches)
+        cudaFree(cv->patches);
+    free(cv);
     free(self);
 }
 
 Module* conv2d_create(Context* ctx, int C_in, int C_out, int K, int stride, int pad, int H, int W, int max_batch,
     int mp_mode, float gain)
 {
-    Module* m = (Module*)calloc(1, sizeof(Module));
-    B200Conv2D* st = (B200Conv2D*)calloc(1, sizeof(B200Conv2D));
-    st->C_in = C_in;
-    st->C_out = C_out;
-    st->K = K;
-    st->stride = stride;
-    st->pad = pad;
-    st->Hi = H;
-    st->Wi = W;
-    st->Ho = (H + 2 * pad - K) / stride + 1;
-    st->Wo = (W + 2 * pad - K) / stride + 1;
-    st->max_batch = max_batch;
-    st->mp_mode = mp_mode;
-    st->pointwise = (K == 1 && stride == 1 && pad == 0);
-    st->eps = 1e-4f;
+    FastConv* cv = (FastConv*)calloc(1, sizeof *cv);
+    ConvShape* sh = &cv->sh;
+    sh->in_h = H; sh->in_w = W; sh->in_c = C_in; sh->out_c = C_out;
+    sh->k = K; sh->stride = stride; sh->pad = pad;
+    sh->out_h = (H + 2 * pad - K) / stride + 1;
+    sh->out_w = (W + 2 * pad - K) / stride + 1;
+    sh->taps_c = K * K * C_in;
+    cv->magnitude_preserving = mp_mode != 0;
+    cv->is_pointwise = (K == 1 && stride == 1 && pad == 0);
+    cv->wn_eps = 1e-4f;
 
-    const int Kg = K * K * C_in;
-    st->Wt = nn_device_alloc((size_t)Kg * C_out);
-    st->gW = nn_device_alloc((size_t)Kg * C_out);
-    if (!st->pointwise)
-        st->col = nn_device_alloc((size_t)max_batch * st->Ho * st->Wo * Kg);
-    st->zero = nn_device_alloc(1);
-    NN_CUDA_CHECK(cudaMemset(st->zero, 0, sizeof(float)));
+    /* parameters and their gradients in one allocation; every piece starts on a 16-byte boundary */
+    const size_t wsize = (size_t)sh->taps_c * C_out, wpad = (wsize + 3) & ~(size_t)3;
+    const size_t esize = mp_mode ? 1 : (size_t)C_out, epad = (esize + 3) & ~(size_t)3;
+    NN_CUDA_CHECK(cudaMalloc((void**)&cv->params, (2 * wpad + 2 * epad + 4) * sizeof(float)));
+    cv->weight = cv->params;
+    cv->weight_grad = cv->weight + wpad;
+    cv->extra = cv->weight_grad + wpad;
+    cv->extra_grad = cv->extra + epad;
+    cv->zero = cv->extra_grad + epad;
+    NN_CUDA_CHECK(cudaMemset(cv->extra, 0, (2 * epad + 4) * sizeof(float)));
+    if (!cv->is_pointwise)
+        NN_CUDA_CHECK(cudaMalloc((void**)&cv->patches, (size_t)max_batch * sh->out_h * sh->out_w * sh->taps_c * sizeof(float)));
 
-    /* same draws from ctx->curand as the reference constructor, so that a model built from the
-       same generator state starts from identical weights */
-    if (mp_mode) {
-        st->gain = nn_device_alloc(1);
-        st->g_gain = nn_device_alloc(1);
-        nn_fill_normal(ctx->curand, st->Wt, (size_t)Kg * C_out, 0.0f, 1.0f);
-        NN_CUDA_CHECK(cudaMemcpy(st->gain, &gain, sizeof(float), cudaMemcpyHostToDevice));
-    } else {
-        st->b = nn_device_alloc((size_t)C_out);
-        st->gb = nn_device_alloc((size_t)C_out);
-        nn_fill_normal(ctx->curand, st->Wt, (size_t)Kg * C_out, 0.0f, sqrtf(2.0f / (float)Kg));
-        NN_CUDA_CHECK(cudaMemset(st->b, 0, (size_t)C_out * sizeof(float)));
-    }
+    /* the same draws from ctx->curand as the reference constructor makes, so that a model built from
+       the same generator state starts from identical weights */
+    const float init_std = mp_mode ? 1.0f : sqrtf(2.0f / (float)sh->taps_c);
+    nn_fill_normal(ctx->curand, cv->weight, wsize, 0.0f, init_std);
+    if (mp_mode)
+        NN_CUDA_CHECK(cudaMemcpy(cv->extra, &gain, sizeof(float), cudaMemcpyHostToDevice));
 
+    Module* m = (Module*)calloc(1, sizeof *m);
     m->name = "conv2d";
     m->in_dim = H * W * C_in;
-    m->out_dim = st->Ho * st->Wo * C_out;
-    m->state = st;
-    m->forward = b200_conv2d_forward;
-    m->backward = b200_conv2d_backward;
-    m->parameters = b200_conv2d_parameters;
-    m->free = b200_conv2d_free;
+    m->out_dim = sh->out_h * sh->out_w * C_out;
+    m->state = cv;
+    m->forward = fastconv_forward;
+    m->backward = fastconv_backward;
+    m->parameters = fastconv_parameters;
+    m->free = fastconv_free;
     return m;
 }

@@ -6,75 +6,81 @@
 #include <stdlib.h>
 
 /* ------------------------------------------------------------------ GroupNorm + activation */
+/* One device allocation per module: [scale | shift | scale grad | shift grad | mean | rstd]; the four
+   channel vectors are padded to 16-byte multiples so that the kernels' 128-bit accesses apply. */
 typedef struct {
-    int C, G, HW;
-    float eps;
+    int channels, groups, pixels;
     Activation act;
-    float *gamma, *beta, *ggamma, *gbeta, *mu, *rstd;
-} GNActState;
+    float epsilon;
+    float* block;
+    float *scale, *shift, *scale_grad, *shift_grad; /* gamma, beta and their gradients */
+    float *mean, *rstd;                               /* [max_batch * groups], written by forward */
+} NormAct;
 
-static void gnact_forward(Module* self, const float* in, float* out, int batch, Context* ctx)
+static void normact_forward(Module* self, const float* x, float* y, int batch, Context* ctx)
 {
-    GNActState* st = (GNActState*)self->state;
-    launch_groupnorm_act_forward(out, st->mu, st->rstd, in, st->gamma, st->beta, batch, st->HW, st->C, st->G,
-        st->eps, st->act, ctx->stream);
+    NormAct* na = (NormAct*)self->state;
+    launch_groupnorm_act_forward(y, na->mean, na->rstd, x, na->scale, na->shift, batch, na->pixels, na->channels,
+        na->groups, na->epsilon, na->act, ctx->stream);
 }
 
-static void gnact_backward(Module* self, const float* in, const float* out, const float* grad_out,
-    float* grad_in, int batch, Context* ctx)
+static void normact_backward(Module* self, const float* x, const float* y, const float* dy, float* dx, int batch,
+    Context* ctx)
 {
-    (void)out; /* the pre-activation is recomputed from in, mu, rstd: nothing is kept from forward */
-    GNActState* st = (GNActState*)self->state;
-    launch_groupnorm_act_backward(grad_in, st->ggamma, st->gbeta, grad_out, in, st->gamma, st->beta, st->mu,
-        st->rstd, batch, st->HW, st->C, st->G, st->act, ctx->stream);
+    (void)y; /* the pre-activation is recomputed from x, mean, rstd: nothing is kept from forward */
+    NormAct* na = (NormAct*)self->state;
+    launch_groupnorm_act_backward(dx, na->scale_grad, na->shift_grad, dy, x, na->scale, na->shift, na->mean, na->rstd,
+        batch, na->pixels, na->channels, na->groups, na->act, ctx->stream);
 }
 
-static void gnact_parameters(Module* self, ParamList* pl)
+static void normact_parameters(Module* self, ParamList* pl)
 {
-    GNActState* st = (GNActState*)self->state;
-    param_list_add(pl, st->gamma, st->ggamma, st->C);
-    param_list_add(pl, st->beta, st->gbeta, st->C);
+    NormAct* na = (NormAct*)self->state;
+    param_list_add(pl, na->scale, na->scale_grad, na->channels);
+    param_list_add(pl, na->shift, na->shift_grad, na->channels);
 }
 
-static void gnact_free(Module* self)
+static void normact_free(Module* self)
 {
-    GNActState* st = (GNActState*)self->state;
-    float* bufs[6] = { st->gamma, st->beta, st->ggamma, st->gbeta, st->mu, st->rstd };
-    for (int i = 0; i < 6; ++i)
-        cudaFree(bufs[i]);
-    free(st);
+    NormAct* na = (NormAct*)self->state;
+    cudaFree(na->block);
+    free(na);
     free(self);
 }
 
 Module* groupnorm_act_create(int C, int num_groups, int H, int W, int max_batch, Activation act)
 {
     NN_ASSERT(num_groups > 0 && C % num_groups == 0, "groupnorm_act: C must be divisible by num_groups");
-    Module* m = (Module*)calloc(1, sizeof(Module));
-    GNActState* st = (GNActState*)calloc(1, sizeof(GNActState));
-    st->C = C;
-    st->G = num_groups;
-    st->HW = H * W;
-    st->eps = 1e-5f;
-    st->act = act;
-    st->gamma = nn_device_alloc((size_t)C);
-    st->beta = nn_device_alloc((size_t)C);
-    st->ggamma = nn_device_alloc((size_t)C);
-    st->gbeta = nn_device_alloc((size_t)C);
-    st->mu = nn_device_alloc((size_t)max_batch * num_groups);
-    st->rstd = nn_device_alloc((size_t)max_batch * num_groups);
-    float* init = (float*)malloc((size_t)C * sizeof(float));
+    NormAct* na = (NormAct*)calloc(1, sizeof *na);
+    na->channels = C;
+    na->groups = num_groups;
+    na->pixels = H * W;
+    na->act = act;
+    na->epsilon = 1e-5f;
+
+    const size_t cpad = ((size_t)C + 3) & ~(size_t)3, stats = (size_t)max_batch * num_groups;
+    NN_CUDA_CHECK(cudaMalloc((void**)&na->block, (4 * cpad + 2 * stats) * sizeof(float)));
+    NN_CUDA_CHECK(cudaMemset(na->block, 0, (4 * cpad + 2 * stats) * sizeof(float))); /* shift = 0 */
+    na->scale = na->block;
+    na->shift = na->scale + cpad;
+    na->scale_grad = na->shift + cpad;
+    na->shift_grad = na->scale_grad + cpad;
+    na->mean = na->shift_grad + cpad;
+    na->rstd = na->mean + stats;
+    float* ones = (float*)malloc((size_t)C * sizeof(float));
     for (int c = 0; c < C; ++c)
-        init[c] = 1.0f;
-    NN_CUDA_CHECK(cudaMemcpy(st->gamma, init, (size_t)C * sizeof(float), cudaMemcpyHostToDevice));
-    NN_CUDA_CHECK(cudaMemset(st->beta, 0, (size_t)C * sizeof(float)));
-    free(init);
+        ones[c] = 1.0f;
+    NN_CUDA_CHECK(cudaMemcpy(na->scale, ones, (size_t)C * sizeof(float), cudaMemcpyHostToDevice));
+    free(ones);
+
+    Module* m = (Module*)calloc(1, sizeof *m);
     m->name = "groupnorm_act";
     m->in_dim = m->out_dim = H * W * C;
-    m->state = st;
-    m->forward = gnact_forward;
-    m->backward = gnact_backward;
-    m->parameters = gnact_parameters;
-    m->free = gnact_free;
+    m->state = na;
+    m->forward = normact_forward;
+    m->backward = normact_backward;
+    m->parameters = normact_parameters;
+    m->free = normact_free;
     return m;
 }
 
