@@ -256,7 +256,7 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
 
 @pytest.mark.parametrize("shape", [dict(B=3, HW=4096, C=32, G=8), dict(B=2, HW=2500, C=48, G=6),
                                    dict(B=80, HW=4100, C=64, G=32)])
-@pytest.mark.parametrize("act", ["silu", None])
+@pytest.mark.parametrize("act", ["silu", "mp_silu", None])
 @pytest.mark.parametrize("bwd_vpt", [8, 4])
 def test_groupnorm_chunked_strips_for_tall_samples(lib, orc, shape, act, bwd_vpt):
     """Samples too tall for the register-resident strips (64x64 images, ragged 50x50, and enough strips
