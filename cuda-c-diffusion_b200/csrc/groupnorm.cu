@@ -1117,15 +1117,21 @@ static bool gn_forward_cstrip(float* y, float* mu, float* rstd, const float* x, 
         StripPlan plan;
         if (!cstrip_plan(&plan, HW, C, G))
             return false;
-        constexpr int VPT = 4, MB = 2;
+        // 4 rows per thread keep the kernel inside 64 registers (two CTAs per SM, no spills); 8 rows double the
+        // bytes each CTA has in flight at the price of a few spilled registers
+        const int VPT = tune_get("gn_fwd_cstrip_vpt", 4) == 8 ? 8 : 4;
+        constexpr int MB = 2;
         const long items = (long)B * plan.g.nct;
         const long resident = (long)sm_count() * MB;
         const long per_cta = (items + resident - 1) / resident;
         const long pgrid = (items + per_cta - 1) / per_cta;
         const int nchunks = (HW + plan.g.RSTEP * VPT - 1) / (plan.g.RSTEP * VPT);
         const size_t psmem = (size_t)VPT * plan.NT * 16 + plan.smem;
-        static bool done[64] = { false };
-        return pstrip_launch(gn_fwd_cstrip<512, VPT, ACT, MB>, done, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
+        static bool done4[64] = { false }, done8[64] = { false };
+        if (VPT == 8)
+            return pstrip_launch(gn_fwd_cstrip<512, 8, ACT, MB>, done8, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
+                plan.g, eps, (int)items, nchunks);
+        return pstrip_launch(gn_fwd_cstrip<512, 4, ACT, MB>, done4, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
             plan.g, eps, (int)items, nchunks);
     }
 }
