@@ -13,6 +13,8 @@
 // (resident CTAs x HW x Ct x 4 bytes per tensor against 126 MB), so DRAM still sees every input
 // byte once; beyond that the strip is read from DRAM twice, which is still fewer bytes and far
 // fewer barriers than the tile kernels need.
+// (A two-deep ring of chunk buffers over a flattened (strip, pass, chunk) sequence was measured:
+// 10 % faster on 128x128 samples, 8-12 % slower on 64x64 ones with an activation; not kept.)
 #pragma once
 
 namespace b200 {
