@@ -484,39 +484,49 @@ def cpu_baseline(threads=None, samples=16, min_seconds=12.0):
 
 
 # ------------------------------------------------------------------------------------ range-sharded optimizer
-def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10):
-    """Optimizer config: flat 64M-parameter vector, fused Adam+EMA on this rank's parameter range, then an
-    in-place NCCL all-gather of the updated parameters.  Returns per-GPU kernel GB/s (36 B/param of the
-    local range) and the time of update+gather."""
+def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10, chunks=4):
+    """Optimizer config: flat 64M-parameter vector, fused Adam+EMA on this rank's share, then an in-place NCCL
+    all-gather of the updated parameters.  Two measurements: the update kernel alone on one contiguous range
+    (per-GPU GB/s at 36 B/param), and update + all-gather with the ownership interleaved over `chunks`
+    super-chunks so that the gather of chunk i overlaps the update of chunk i+1."""
     sh = importlib.import_module("cuda-c-diffusion_b200.sharding")
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(7)  # same seed everywhere: replicated parameters
     p = 0.02 * torch.randn(npar, device=dev, generator=g)
     grad = 1e-3 * torch.randn(npar, device=dev, generator=g)
-    opt = sh.ShardedAdamEMA(p, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, decay=0.999)
-    for _ in range(3):
-        opt.step(grad, grad_scale=1.0 / world)
-    torch.cuda.synchronize()
-    if world > 1:
-        torch.distributed.barrier()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    t_kernel = t_total = 0.0
-    for _ in range(iters):
-        ev[0].record()
-        opt.step(grad, grad_scale=1.0 / world, gather=False)
-        ev[1].record()
-        opt.all_gather()
-        ev[2].record()
+    kw = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, decay=0.999)
+
+    def timed(opt, gather):
+        for _ in range(3):
+            opt.step(grad, grad_scale=1.0 / world, gather=gather)
         torch.cuda.synchronize()
-        t_kernel += ev[0].elapsed_time(ev[1])
-        t_total += ev[0].elapsed_time(ev[2])
-    t = torch.tensor([t_kernel / iters, t_total / iters], device=dev)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    kern_ms, tot_ms = float(t[0]), float(t[1])
-    return {"params": npar, "shard": opt.shard, "kernel_ms": round(kern_ms, 4), "update_plus_allgather_ms": round(tot_ms, 4),
-            "kernel_GBps_per_gpu": round(36 * opt.shard / (kern_ms * 1e-3) / 1e9, 1),
-            "allgather_GBps_per_gpu_in": round((world - 1) * opt.shard * 4 / max((tot_ms - kern_ms) * 1e-3, 1e-9) / 1e9, 1)
+        if world > 1:
+            torch.distributed.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for _ in range(iters):
+            e0.record()
+            opt.step(grad, grad_scale=1.0 / world, gather=gather)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        t = torch.tensor([total / iters], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t[0])
+
+    opt = sh.ShardedAdamEMA(p.clone(), **kw)
+    kern_ms = timed(opt, gather=False)
+    seq_ms = timed(opt, gather=True)
+    shard = opt.shard
+    del opt
+    opt = sh.ShardedAdamEMA(p.clone(), chunks=chunks if world > 1 else 1, **kw)
+    tot_ms = timed(opt, gather=True)
+    return {"params": npar, "shard": shard, "kernel_ms": round(kern_ms, 4),
+            "kernel_GBps_per_gpu": round(36 * shard / (kern_ms * 1e-3) / 1e9, 1),
+            "update_then_allgather_ms": round(seq_ms, 4), "update_plus_allgather_ms": round(tot_ms, 4),
+            "chunks": chunks if world > 1 else 1,
+            "allgather_GBps_per_gpu_in": round((world - 1) * shard * 4 / max((seq_ms - kern_ms) * 1e-3, 1e-9) / 1e9, 1)
             if world > 1 else None}
 
 
