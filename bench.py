@@ -108,9 +108,12 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------ libraries
-def load_b200():
-    capi = importlib.import_module("cuda-c-diffusion_b200.capi")
-    return capi.load(), capi
+def load_capi():
+    """The binding table only (signatures of the launcher set); loads no shared object."""
+    return importlib.import_module("cuda-c-diffusion_b200.capi")
+
+
+BIN = ROOT / "cuda-c-diffusion_b200" / "build" / "bin"  # host programs (cuda-c-diffusion_b200/csrc/host/Makefile)
 
 
 def load_reference(capi):
@@ -205,15 +208,12 @@ class Step:
                 self.pending[i] = None
 
 
-def timed_steps(step, steps, warmup, world):
-    for _ in range(warmup):
-        step.run()
-        step.exchange()
-    step.finish()
+def timed_block(step, steps, world):
+    """EXACTLY `steps` steps between two events, bracketed by barrier + synchronize on both sides; returns the
+    block's milliseconds (max over ranks) and the per-kernel milliseconds per step of this rank."""
     torch.cuda.synchronize()
     if world > 1:
         torch.distributed.barrier()
-    per_kernel = [0.0] * len(Step.KERNELS)
     all_marks = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -229,6 +229,7 @@ def timed_steps(step, steps, warmup, world):
     if world > 1:
         torch.distributed.barrier()
     ms = e0.elapsed_time(e1)
+    per_kernel = [0.0] * len(Step.KERNELS)
     for marks in all_marks:
         for i in range(len(Step.KERNELS)):
             per_kernel[i] += marks[i].elapsed_time(marks[i + 1])
@@ -238,6 +239,19 @@ def timed_steps(step, steps, warmup, world):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t.item())
     return ms, per_kernel
+
+
+def timed_steps(step, steps, warmup, world, blocks=5):
+    """`warmup` untimed steps, then `blocks` timed blocks of exactly `steps` steps each; the reported block is the
+    median one (one block of 20 steps lasts about 10 ms, too short a window to trust alone)."""
+    for _ in range(warmup):
+        step.run()
+        step.exchange()
+    step.finish()
+    runs = [timed_block(step, steps, world) for _ in range(max(1, blocks))]
+    order = sorted(range(len(runs)), key=lambda i: runs[i][0])
+    ms, per_kernel = runs[order[len(order) // 2]]
+    return ms, per_kernel, [round(r[0], 4) for r in runs]
 
 
 def e2e_steps(step, steps, warmup, world):
@@ -373,6 +387,7 @@ def ops_table(lib, fused, peak):
         if nbytes:
             rec["GBps"] = round(nbytes / secs / 1e9, 1)
             rec["frac_of_measured_peak"] = round(nbytes / secs / 1e9 / peak, 3)
+            rec["frac_of_nominal_8TBs"] = round(nbytes / secs / 1e9 / 8000.0, 3)
         out[name] = rec
 
     # ---- config 0: GroupNorm fwd+bwd [128,28,28,64], G=32 (25.7 MB tensors: rotate 8 sets to defeat L2)
@@ -443,16 +458,15 @@ def ops_table(lib, fused, peak):
 
 
 # ------------------------------------------------------------------------------------ CPU baseline
-def cpu_baseline(threads=None, samples=16, min_seconds=12.0):
+def cpu_baseline(threads=None, samples=16, min_seconds=10.0, single_seconds=6.0):
     """The plain-C port (oracle/layer_oracle.c, fp32 accumulation) on the host cores over a bounded
     sample of the step: `samples` of the 256 images per GPU, same kernel sequence, repeated until
-    about `min_seconds` of CPU time have been spent."""
+    about `min_seconds` of wall time with every host thread, then about `single_seconds` with one."""
     sys.path.insert(0, str(ROOT / "oracle"))
     orc = importlib.import_module("oracle")
     orc.load()
     orc.set_accumulate_double(False)
     threads = threads or orc.max_threads()
-    orc.set_threads(threads)
     rng = np.random.default_rng(0)
     x = rng.standard_normal((samples, HW, C), dtype=np.float32)
     dy = rng.standard_normal((samples, HW, C), dtype=np.float32)
@@ -466,20 +480,27 @@ def cpu_baseline(threads=None, samples=16, min_seconds=12.0):
         orc.layernorm_backward(dy.reshape(-1, C), x.reshape(-1, C), gam, lmu, lrs)
         orc.sinusoidal(tt, EMB, np.float32(math.log(1e4)))
 
-    one()  # warm-up (page faults, thread pool)
-    reps, t0 = 0, time.perf_counter()
-    while True:
-        one()
-        reps += 1
-        dt = time.perf_counter() - t0
-        if dt >= min_seconds or reps >= 5000:
-            break
-    nbytes = STEP_BYTES * samples / B * reps
+    def timed(nthreads, seconds):
+        orc.set_threads(nthreads)
+        one()  # warm-up (page faults, thread pool)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            one()
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt >= seconds or reps >= 5000:
+                break
+        return STEP_BYTES * samples / B * reps / dt / 1e9, reps, dt
+
+    gbs, reps, dt = timed(threads, min_seconds)
+    gbs1, reps1, dt1 = timed(1, single_seconds)
     orc.set_accumulate_double(True)
     orc.set_threads(1)
-    return {"value": round(nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "single_thread": {"value": round(gbs1, 3), "unit": "GB/s", "cores": 1,
+                              "sample": f"same sample x {reps1} repeats, {dt1:.1f} s"},
             "sample": f"{samples} of the {B} samples of one step (same kernel sequence) x {reps} repeats, {dt:.1f} s of "
-                      f"CPU work, OpenMP over {threads} threads; the reference has no CPU path, so this is the "
+                      f"wall time, OpenMP over {threads} threads; the reference has no CPU path, so this is the "
                       f"plain-C port of its kernels"}
 
 
@@ -516,7 +537,27 @@ def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10, chunks=4):
         return float(t[0])
 
     opt = sh.ShardedAdamEMA(p.clone(), **kw)
-    kern_ms = timed(opt, gather=False)
+    # the update kernel alone: pre-sliced views, events around the launch only (no host-side slicing inside)
+    ops = importlib.import_module("cuda-c-diffusion_b200.ops")
+    opt.t = 3
+    hy = opt.hyper(1.0 / world)
+    own = opt.params[opt.lo:opt.hi]
+    gown = grad[opt.lo:opt.hi].contiguous() if opt.hi <= grad.numel() else opt._grad_piece(grad, opt.lo, opt.hi)
+    call = lambda: ops.adam_ema_step_(own, opt.m, opt.v, opt.shadow, gown, hy.lr, hy.beta1, hy.beta2, hy.eps, hy.bc1,
+                                      hy.bc2, hy.decay, hy.grad_scale)
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        call()
+        b.record()
+    torch.cuda.synchronize()
+    kt = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / iters], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(kt, op=torch.distributed.ReduceOp.MAX)
+    kern_ms = float(kt[0])
     seq_ms = timed(opt, gather=True)
     shard = opt.shard
     del opt
@@ -549,7 +590,26 @@ def write_edm_config(folder, batch, train_steps):
     return ini
 
 
-def edm_train_images_per_s(binary, batch=256, steps=(50, 450)):
+def write_ddpm_config(folder, batch, train_steps):
+    """Synthetic image file and an .ini for the reference's DDPM trainer (ddpm/main_ddpm.c): the model of its own
+    ddpm.ini (channels 32/64/128, emb 64, 4 heads, 32 groups, T=1000, min-SNR gamma 5), batch `batch`, TF32 GEMMs."""
+    os.makedirs(folder, exist_ok=True)
+    images = os.path.join(folder, "images.bin")
+    if not os.path.exists(images):
+        rng = np.random.default_rng(0)
+        n = 4096
+        img = np.where(rng.random((n, 28, 28)) < 0.8, -1.0, rng.uniform(-1, 1, (n, 28, 28))).astype(np.float32)
+        img.tofile(images)
+    ini = os.path.join(folder, f"ddpm_{train_steps}.ini")
+    with open(ini, "w") as f:
+        f.write(f"channels = 32,64,128\nemb_dim = 64\nheads = 4\nnum_groups = 32\nbatch_size = {batch}\n"
+                f"train_steps = {train_steps}\nlr = 1e-3\nlr_warmup = 500\nlr_ref = 2000\nsnr_gamma = 5.0\n"
+                f"ema_decay = 0.999\nT = 1000\nbeta_start = 1e-4\nbeta_end = 0.02\nddim_steps = 1\ntf32 = 1\n"
+                f"images = {images}\nH = 28\nW = 28\nC = 1\n")
+    return ini
+
+
+def edm_train_images_per_s(binary, batch=256, steps=(50, 450), write_config=None):
     """Images/s of the reference's own EDM trainer (edm/main_edm.c + diffusion/train.c + every host module,
     unmodified) with the given kernel backend linked in.  Config: channels 64/128/128, emb 128, 1 head, t 0.3,
     batch 256, Adam lr 1e-3, EMA 0.999, TF32 GEMMs, synthetic 28x28 images (pixel -1 with p=0.8, else U(-1,1)).
@@ -560,7 +620,7 @@ def edm_train_images_per_s(binary, batch=256, steps=(50, 450)):
     with tempfile.TemporaryDirectory() as tmp:
         times = []
         for st in (2,) + tuple(steps):  # the first (2-step) run only warms caches and is not used
-            ini = write_edm_config(tmp, batch, st)
+            ini = (write_config or write_edm_config)(tmp, batch, st)
             t0 = time.perf_counter()
             res = subprocess.run([str(binary), ini], cwd=tmp, capture_output=True, text=True, timeout=900)
             times.append(time.perf_counter() - t0)
@@ -573,16 +633,22 @@ def edm_train_images_per_s(binary, batch=256, steps=(50, 450)):
 
 
 def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True, fastconv=True):
-    """Data-parallel EDM UNet training (oracle/_ref/edm_dp_train[_fastconv]: the reference's UNet and host
+    """Data-parallel EDM UNet training (build/bin/edm_dp_train[_fastconv]: the reference's UNet and host
     modules, this library's kernels, NCCL gradient all-reduce; `fastconv` links csrc/host/b200_conv2d.c in place of
     the reference's conv2d.c).  Every rank of this benchmark starts one trainer process on its own GPU; the
     trainers find each other through a file named after MASTER_PORT.  Rank 0 returns the trainer's JSON
     (device-timed, max over ranks), the other ranks None."""
-    exe = ROOT / "oracle" / "_ref" / ("edm_dp_train_fastconv" if fastconv else "edm_dp_train")
+    exe = BIN / ("edm_dp_train_fastconv" if fastconv else "edm_dp_train")
     if not exe.exists():
         return None
     env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local_rank))
-    id_file = f"/tmp/edm_dp_train_{os.environ.get('MASTER_PORT', '0')}_{batch_per_gpu}_{int(fastconv)}.ncclid"
+    # the trainers of one run meet through a file; its name carries a per-run nonce chosen by rank 0, so that a
+    # file left behind by a crashed or killed earlier run (or another job on the machine) is never picked up
+    nonce = [f"{os.getpid()}_{time.time_ns()}"]
+    if world > 1:
+        torch.distributed.broadcast_object_list(nonce, src=0)
+    import tempfile
+    id_file = os.path.join(tempfile.gettempdir(), f"edm_dp_train_{nonce[0]}_{batch_per_gpu}_{int(fastconv)}.ncclid")
     cmd = [str(exe), "--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup), "--id-file", id_file]
     if graph:
         cmd.append("--graph")
@@ -590,6 +656,9 @@ def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, gra
         res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=90)
     except subprocess.TimeoutExpired:
         return {"error": "timeout"} if rank == 0 else None
+    finally:
+        if rank == 0 and os.path.exists(id_file):
+            os.unlink(id_file)
     if rank != 0:
         return None
     if res.returncode != 0:
@@ -619,6 +688,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--blocks", type=int, default=5, help="timed blocks of --steps steps; the median block is reported")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
@@ -654,10 +724,13 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    lib, capi = load_b200()
-    for kv in args.tune:
-        key, val = kv.split("=")
-        lib.b200_tune_set(key.encode(), int(val))
+    capi = load_capi()
+    lib = None
+    if args.impl == "b200":  # the reference arm never maps this repository's kernel library
+        lib = capi.load()
+        for kv in args.tune:
+            key, val = kv.split("=")
+            lib.b200_tune_set(key.encode(), int(val))
     peak, peak_src = measured_peak()
     fused = True
     ref_note = None
@@ -683,10 +756,10 @@ def main():
     step = Step(lib_run, fused, torch.device("cuda", local), seed=1234 + rank)
     launches0 = lib.b200_launch_count() if args.impl == "b200" else 0
     with ClockSampler(local) as cs:
-        ms, per_kernel = timed_steps(step, args.steps, args.warmup, world)
+        ms, per_kernel, block_ms = timed_steps(step, args.steps, args.warmup, world, args.blocks)
     launches = (lib.b200_launch_count() - launches0) if args.impl == "b200" else None
-    if launches is not None:
-        launches = int(launches * args.steps / (args.steps + args.warmup))
+    if launches is not None:  # launches of ONE timed block of `steps` steps
+        launches = int(launches * args.steps / (args.steps * max(1, args.blocks) + args.warmup))
     clocks = cs.summary()
     e2e_k = max(3, min(args.steps, 10))
     if args.no_e2e:
@@ -709,12 +782,14 @@ def main():
                    "algorithmic_bytes_per_step": STEP_BYTES, "seed": 1234,
                    "exchange": "all-reduce of the 4*C parameter-gradient floats, overlapped with the next step (N>1)"},
         "clocks": clocks,
+        "timing": {"blocks_ms": block_ms, "reported": "median block of exactly `steps` steps, CUDA events, max over ranks"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_k, "ms_per_step": round(e2e_ms / e2e_k, 3),
                 "how": "C ABI on host buffers; upload, compute and download streams over two device buffer sets"},
         "kernels_ms": {k: round(v, 4) for k, v in zip(Step.KERNELS, per_kernel)},
         "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 3), "traffic": NCU_TRAFFIC.get(dom_name), "peak_source": peak_src,
+                     "frac": round(achieved / peak, 3), "frac_of_nominal_8TBs": round(achieved / 8000.0, 3),
+                     "traffic": NCU_TRAFFIC.get(dom_name), "peak_source": peak_src,
                      "all": {k: round(KERNEL_BYTES[k] / (v * 1e-3) / 1e9 / peak, 3)
                              for k, v in zip(Step.KERNELS[:-1], per_kernel)}},
     }
@@ -746,10 +821,22 @@ def main():
             step = None
             torch.cuda.empty_cache()
             line["ops"] = ops_table(lib_run, fused, peak)
-            exe = ROOT / "oracle" / "_ref" / ("edm_demo_b200" if args.impl == "b200" else "edm_demo_ref")
+            exe = BIN / "edm_demo_b200" if args.impl == "b200" else ROOT / "oracle" / "_ref" / "edm_demo_ref"
             edm = None if args.no_trainer else edm_train_images_per_s(exe)
             if edm is not None:
                 line["edm_unet_train"] = edm
+            # the reference's DDPM trainer (GroupNorm+SiLU blocks): its own kernels in the reference arm; in this
+            # arm once as a plain drop-in at the launch_* ABI and once with the fused residual block linked in
+            if not args.no_trainer:
+                if args.impl == "b200":
+                    ddpm = {"drop_in": edm_train_images_per_s(BIN / "ddpm_demo_b200", steps=(20, 120),
+                                                              write_config=write_ddpm_config),
+                            "fused_block": edm_train_images_per_s(BIN / "ddpm_demo_b200_fused", steps=(20, 120),
+                                                                  write_config=write_ddpm_config)}
+                else:
+                    ddpm = edm_train_images_per_s(ROOT / "oracle" / "_ref" / "ddpm_demo_ref", steps=(20, 120),
+                                                  write_config=write_ddpm_config)
+                line["ddpm_unet_train"] = ddpm
         print(json.dumps(line))
     if world > 1:
         torch.distributed.barrier()

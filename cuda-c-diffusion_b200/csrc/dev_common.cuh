@@ -79,6 +79,10 @@ struct Scratch {
     unsigned int* tickets; // at least `ntickets` counters, all zero between kernels
 };
 bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out);
+// out[c] = sum over `nparts` partial rows of `width` floats, fixed order; columns below `split`
+// go to out_a, the rest to out_b (rownorm.cu).
+void fold_partials(float* out_a, float* out_b, const float* partials, int nparts, int width, int split,
+    cudaStream_t s);
 // Device address of the error word that kernels set when a bounded wait runs
 // out (0 = healthy); one word per device.
 int* device_error_word();

@@ -1248,7 +1248,7 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     if (gn_backward_tile<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
         return;
     Scratch sc;
-    B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed");
+    B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
     B200_REQUIRE(B <= 65535, "groupnorm_backward: batch %d too large for the generic path", B);
     gn_bwd_dx_generic<ACT><<<B * G, GN_GENERIC_THREADS, 0, s>>>(dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
     count_launch();

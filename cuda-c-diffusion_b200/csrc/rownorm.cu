@@ -499,7 +499,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
     if (fast_rows_ok(C) && rows > 0 && aligned16(grad_in) && aligned16(grad_out) && aligned16(x) && aligned16(gamma)) {
         const int R = (C / 128 == 1) ? 4 : (C / 128 == 2 ? 2 : 1);
         const int grid = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 4);
-        B200_REQUIRE(scratch_get(s, (size_t)grid * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed");
+        B200_REQUIRE(scratch_get(s, (size_t)grid * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
         RN_DISPATCH_VPT(C, (layernorm_bwd_rows<VPT, R><<<grid, RN_THREADS, 0, s>>>(grad_in, sc.partials, grad_out, x,
                                 gamma, mu, rstd, rows)));
         count_launch();
@@ -516,7 +516,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
     const int chunk_rows = 256;
     const int nchunks = rows > 0 ? (int)((rows + chunk_rows - 1) / chunk_rows) : 1;
     B200_REQUIRE(nchunks <= 65535, "layernorm_backward: too many rows for the generic path");
-    B200_REQUIRE(scratch_get(s, (size_t)nchunks * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed");
+    B200_REQUIRE(scratch_get(s, (size_t)nchunks * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
     layernorm_bwd_param_generic<<<dim3((C + 31) / 32, nchunks), dim3(32, 8), 0, s>>>(sc.partials, grad_out, x, mu,
         rstd, rows, C, chunk_rows);
     count_launch();

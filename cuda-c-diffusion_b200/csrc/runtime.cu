@@ -96,6 +96,16 @@ struct Arena {
     size_t ntickets = 0;
 };
 static std::map<std::pair<int, cudaStream_t>, Arena> g_arenas;
+// Blocks that an arena has outgrown.  They are never released: a CUDA graph captured while a
+// block was current keeps its address and may be replayed at any later time.
+static std::vector<void*> g_retired;
+
+// True while `s` is being captured into a graph (an allocation is not allowed then).
+static bool stream_is_capturing(cudaStream_t s)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    return cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
+}
 
 bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out)
 {
@@ -105,18 +115,22 @@ bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out)
     std::lock_guard<std::mutex> lk(g_mu);
     Arena& a = g_arenas[std::make_pair(dev, s)];
     if (a.floats < floats) {
-        // Growing: the old block may still be in use by kernels in flight on
-        // this stream, so it is released with the stream-ordered free.
+        // Growing.  Refused during stream capture (reserve the arena before capturing); the old
+        // block is retired, not freed: kernels in flight and graphs captured earlier still use it.
+        if (stream_is_capturing(s))
+            return false;
         size_t want = floats < (1u << 18) ? (1u << 18) : floats;
         float* np = nullptr;
         if (cudaMalloc(&np, want * sizeof(float)) != cudaSuccess)
             return false;
         if (a.partials)
-            cudaFreeAsync(a.partials, s);
+            g_retired.push_back(a.partials);
         a.partials = np;
         a.floats = want;
     }
     if (a.ntickets < ntickets) {
+        if (stream_is_capturing(s))
+            return false;
         size_t want = ntickets < 4096 ? 4096 : ntickets;
         unsigned int* nt = nullptr;
         if (cudaMalloc(&nt, want * sizeof(unsigned int)) != cudaSuccess)
@@ -124,7 +138,7 @@ bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out)
         if (cudaMemsetAsync(nt, 0, want * sizeof(unsigned int), s) != cudaSuccess)
             return false;
         if (a.tickets)
-            cudaFreeAsync(a.tickets, s);
+            g_retired.push_back(a.tickets);
         a.tickets = nt;
         a.ntickets = want;
     }

@@ -324,11 +324,14 @@ __global__ void __launch_bounds__(256) softmax_xent_kernel(float* __restrict__ g
 // ---------------------------------------------------------------------------
 template <int MODE>
 __global__ void __launch_bounds__(256) strip_reduce_kernel(float* __restrict__ out, float* __restrict__ gin,
-    const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ cond, int rows_per_group, int C)
+    const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ cond, int rows_per_group, int C,
+    long total_rows)
 {
     __shared__ float part[8][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     const long r0 = (long)blockIdx.y * rows_per_group;
+    if (r0 + rows_per_group > total_rows)  // ragged last group (bias_grad splits the rows evenly)
+        rows_per_group = total_rows > r0 ? (int)(total_rows - r0) : 0;
     float acc = 0.0f;
     if (col < C) {
         const float mod = MODE == 1 ? cond[(size_t)blockIdx.y * C + col] + 1.0f : 0.0f;
@@ -554,7 +557,7 @@ void launch_spatial_modulate_backward(float* grad_in, float* grad_cond, const fl
     if (batch == 0)
         return;
     strip_reduce_kernel<1><<<dim3((C + 31) / 32, batch), dim3(32, 8), 0, s>>>(grad_cond, grad_in, grad_out, in, cond,
-        H * W, C);
+        H * W, C, (long)batch * H * W);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -565,7 +568,7 @@ void launch_spatial_reduce_sum(float* out, const float* in, int batch, int HW, i
     if (batch == 0)
         return;
     strip_reduce_kernel<0><<<dim3((C + 31) / 32, batch), dim3(32, 8), 0, s>>>(out, nullptr, in, nullptr, nullptr, HW,
-        C);
+        C, (long)batch * HW);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -573,10 +576,30 @@ void launch_spatial_reduce_sum(float* out, const float* in, int batch, int HW, i
 void launch_bias_grad(float* gb, const float* grad_out, int batch, int N, cudaStream_t s)
 {
     B200_REQUIRE(batch >= 0 && N > 0, "bias_grad: batch=%d N=%d", batch, N);
-    strip_reduce_kernel<0><<<dim3((N + 31) / 32, 1), dim3(32, 8), 0, s>>>(gb, nullptr, grad_out, nullptr, nullptr,
-        batch, N);
+    // Column sums of a [batch, N] matrix (reference: one thread per column walking every row,
+    // src/kernels.cu:148-161).  The rows are split over enough CTAs to fill the chip; each writes one
+    // partial row and a fixed-order fold adds them, so the result does not depend on scheduling.
+    const int col_ctas = (N + 31) / 32;
+    long want = ((long)sm_count() * 4 + col_ctas - 1) / col_ctas;  // row groups for ~4 CTAs per SM
+    const long most = ((long)batch + 63) / 64;                      // at least 64 rows per group
+    if (want > most)
+        want = most;
+    if (want <= 1) {
+        strip_reduce_kernel<0><<<dim3(col_ctas, 1), dim3(32, 8), 0, s>>>(gb, nullptr, grad_out, nullptr, nullptr, batch,
+            N, (long)batch);
+        count_launch();
+        B200_CHECK_LAUNCH();
+        return;
+    }
+    const int groups = (int)want;
+    const int per = (batch + groups - 1) / groups;
+    Scratch sc;
+    B200_REQUIRE(scratch_get(s, (size_t)groups * N, 0, &sc), "bias_grad: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
+    strip_reduce_kernel<0><<<dim3(col_ctas, groups), dim3(32, 8), 0, s>>>(sc.partials, nullptr, grad_out, nullptr,
+        nullptr, per, N, (long)batch);
     count_launch();
     B200_CHECK_LAUNCH();
+    fold_partials(gb, gb, sc.partials, groups, N, N, s);
 }
 
 void launch_mse_fwd_bwd(float* grad, float* loss_row, const float* pred, const float* target, int batch, int dim,

@@ -149,17 +149,24 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def gpu_run(lib, op, p, inp, fused):
+def gpu_run(lib, op, p, inp, fused, device_out=False):
     """Runs `op` through the C ABI of `lib` on cuda:0.  With fused=False only the
     reference launcher set is used (GroupNorm then activation, Adam then EMA as
-    the reference's host code composes them)."""
+    the reference's host code composes them).  Inputs may be host arrays or device
+    tensors (never modified: in-place launchers work on a copy); with device_out the
+    results stay on the device as tensors (the full-size cases compare there)."""
     import torch
 
     dev = torch.device("cuda:0")
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    T = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(dev)
+
+    def T(a):
+        if isinstance(a, torch.Tensor):
+            return a.to(dev, torch.float32).contiguous().clone()
+        return torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(dev)
+
     E = lambda *shape: torch.empty(*shape, device=dev, dtype=torch.float32)
-    N = lambda t: t.cpu().numpy()
+    N = (lambda t: t) if device_out else (lambda t: t.cpu().numpy())
     F = ctypes.c_float
 
     if op == "act":

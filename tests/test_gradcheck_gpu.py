@@ -1,6 +1,6 @@
 """Runs the reference's own finite-difference test (tests/gradcheck.c, unmodified,
 with its unmodified host modules) linked against this library's kernels.  The
-binary is built by oracle/Makefile where the reference sources are mounted."""
+binaries are built by cuda-c-diffusion_b200/csrc/host/Makefile where the reference sources are available."""
 import subprocess
 from pathlib import Path
 
@@ -8,6 +8,7 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "cuda-c-diffusion_b200" / "build" / "bin"  # built by cuda-c-diffusion_b200/csrc/host/Makefile
 
 
 def _run(exe):
@@ -17,7 +18,7 @@ def _run(exe):
 
 
 def test_reference_gradcheck_passes_with_our_kernels():
-    res = _run(ROOT / "oracle" / "_ref" / "gradcheck_b200")
+    res = _run(BIN / "gradcheck_b200")
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "ALL GRADIENTS OK" in res.stdout
@@ -27,7 +28,7 @@ def test_reference_gradcheck_passes_with_our_kernels():
 def test_c_host_modules_of_fused_entry_points():
     """csrc/host/b200_fused_modules.c (Module vtable + public optimizer/EMA API of the reference)
     against the reference's own host modules and central differences; see tests/host/."""
-    res = _run(ROOT / "oracle" / "_ref" / "fused_modules_check")
+    res = _run(BIN / "fused_modules_check")
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "0 failure(s)" in res.stdout
@@ -37,8 +38,8 @@ def test_c_host_modules_of_fused_entry_points():
 def test_edm_dp_step_matches_reference_step():
     """csrc/host/edm_dp_train.c --check: the batched data-parallel step against the reference's own
     edm_loss_step + optimizer_step + ema_update from identical state (fp32 GEMMs, two steps)."""
-    res = subprocess.run([str(ROOT / "oracle" / "_ref" / "edm_dp_train"), "--check"], capture_output=True, text=True,
-                         timeout=600) if (ROOT / "oracle" / "_ref" / "edm_dp_train").exists() else None
+    res = subprocess.run([str(BIN / "edm_dp_train"), "--check"], capture_output=True, text=True,
+                         timeout=600) if (BIN / "edm_dp_train").exists() else None
     if res is None:
         pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
     print(res.stdout[-3000:])
@@ -52,7 +53,7 @@ def test_edm_dp_two_ranks_stay_in_sync(tmp_path):
     import json
     import os
     import torch
-    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+    exe = BIN / "edm_dp_train"
     if not exe.exists():
         pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
     if torch.cuda.device_count() < 2:
@@ -79,7 +80,7 @@ def test_edm_dp_two_ranks_stay_in_sync(tmp_path):
 
 def test_reference_gradcheck_passes_with_replaced_conv2d_host_module():
     """The reference's gradcheck with its conv2d.c replaced at link time by csrc/host/b200_conv2d.c."""
-    res = _run(ROOT / "oracle" / "_ref" / "gradcheck_b200_fastconv")
+    res = _run(BIN / "gradcheck_b200_fastconv")
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "ALL GRADIENTS OK" in res.stdout
@@ -92,7 +93,7 @@ def test_replaced_conv2d_trains_to_the_same_parameters(tmp_path):
     import numpy as np
     outs = {}
     for name in ("edm_dp_train", "edm_dp_train_fastconv"):
-        exe = ROOT / "oracle" / "_ref" / name
+        exe = BIN / name
         if not exe.exists():
             pytest.skip(f"{name} not built (needs the reference sources at build time)")
         dump = tmp_path / (name + ".bin")
@@ -111,7 +112,7 @@ def test_edm_dp_checkpoint_round_trip(tmp_path):
     (and optimizer/EMA state) exactly and training continues from there."""
     import json
     import numpy as np
-    exe = ROOT / "oracle" / "_ref" / "edm_dp_train_fastconv"
+    exe = BIN / "edm_dp_train_fastconv"
     if not exe.exists():
         pytest.skip("edm_dp_train_fastconv not built (needs the reference sources at build time)")
     ck, d_a, d_b, d_c = (str(tmp_path / n) for n in ("state.ckpt", "a.bin", "b.bin", "c.bin"))
@@ -134,7 +135,7 @@ def test_edm_dp_missing_peer_ends_with_an_error_not_a_hang(tmp_path):
     The rank must give up after its bounded wait with a clear message; nothing has touched the device."""
     import os
     import time
-    exe = ROOT / "oracle" / "_ref" / "edm_dp_train"
+    exe = BIN / "edm_dp_train"
     if not exe.exists():
         pytest.skip("edm_dp_train not built (needs the reference sources at build time)")
     env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="0", EDM_DP_ID_WAIT_S="1.5")

@@ -115,3 +115,27 @@ def test_weight_norm_and_adam_oracles_against_numpy(orc):
     assert np.allclose(p1, pp, atol=1e-6) and np.allclose(s1, 0.99 * p + 0.01 * pp, atol=1e-6)
     a, b = orc.mp_cat(p.reshape(10, 10), g.reshape(10, 10), 0.5)[:, :10], None
     assert np.allclose(a, p.reshape(10, 10), atol=1e-6)  # t=0.5 with equal widths: unit weights
+
+
+# ---- the launchers either side of the fused layer kernels (im2col/col2im, resampling, attention glue,
+# ---- FiLM, bias and loss helpers): the oracle against golden outputs of the reference's kernels
+import plain_cases as pc  # noqa: E402
+
+GOLDEN_PLAIN = Path(__file__).resolve().parent / "golden" / "reference_plain_launchers.npz"
+
+
+@pytest.fixture(scope="module")
+def golden_plain():
+    if not GOLDEN_PLAIN.exists():
+        pytest.skip("golden file not generated yet")
+    return np.load(GOLDEN_PLAIN)
+
+
+@pytest.mark.parametrize("name,fn,args,tol", pc.PLAIN_CASES, ids=[c[0] for c in pc.PLAIN_CASES])
+def test_plain_launcher_oracle_matches_reference_kernel_outputs(orc, golden_plain, name, fn, args, tol):
+    arrays, _ = pc.materialise(name, args)
+    flat = np.concatenate([np.ravel(v).astype(np.float64) for v in arrays.values()])
+    assert np.allclose(golden_plain[f"{name}/__input_sum"], [flat.sum(), np.abs(flat).sum()], rtol=1e-12), \
+        "seeded inputs differ from the ones the golden file was generated with"
+    got = pc.run_oracle(orc, name, fn, args)
+    pc.compare(got, {k: golden_plain[f"{name}/{k}"] for k in got}, tol, "oracle/" + name)
