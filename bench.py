@@ -505,70 +505,44 @@ def cpu_baseline(threads=None, samples=16, min_seconds=10.0, single_seconds=6.0)
 
 
 # ------------------------------------------------------------------------------------ range-sharded optimizer
-def sharded_adam_ema(lib, world, rank, npar=64 * 2 ** 20, iters=10, chunks=4):
-    """Optimizer config: flat 64M-parameter vector, fused Adam+EMA on this rank's share, then an in-place NCCL
-    all-gather of the updated parameters.  Two measurements: the update kernel alone on one contiguous range
-    (per-GPU GB/s at 36 B/param), and update + all-gather with the ownership interleaved over `chunks`
-    super-chunks so that the gather of chunk i overlaps the update of chunk i+1."""
-    sh = importlib.import_module("cuda-c-diffusion_b200.sharding")
-    dev = torch.device("cuda", torch.cuda.current_device())
-    g = torch.Generator(device=dev).manual_seed(7)  # same seed everywhere: replicated parameters
-    p = 0.02 * torch.randn(npar, device=dev, generator=g)
-    grad = 1e-3 * torch.randn(npar, device=dev, generator=g)
-    kw = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, decay=0.999)
-
-    def timed(opt, gather):
-        for _ in range(3):
-            opt.step(grad, grad_scale=1.0 / world, gather=gather)
-        torch.cuda.synchronize()
-        if world > 1:
-            torch.distributed.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        total = 0.0
-        for _ in range(iters):
-            e0.record()
-            opt.step(grad, grad_scale=1.0 / world, gather=gather)
-            e1.record()
-            torch.cuda.synchronize()
-            total += e0.elapsed_time(e1)
-        t = torch.tensor([total / iters], device=dev)
-        if world > 1:
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        return float(t[0])
-
-    opt = sh.ShardedAdamEMA(p.clone(), **kw)
-    # the update kernel alone: pre-sliced views, events around the launch only (no host-side slicing inside)
-    ops = importlib.import_module("cuda-c-diffusion_b200.ops")
-    opt.t = 3
-    hy = opt.hyper(1.0 / world)
-    own = opt.params[opt.lo:opt.hi]
-    gown = grad[opt.lo:opt.hi].contiguous() if opt.hi <= grad.numel() else opt._grad_piece(grad, opt.lo, opt.hi)
-    call = lambda: ops.adam_ema_step_(own, opt.m, opt.v, opt.shadow, gown, hy.lr, hy.beta1, hy.beta2, hy.eps, hy.bc1,
-                                      hy.bc2, hy.decay, hy.grad_scale)
-    for _ in range(3):
-        call()
-    torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
-    for a, b in ev:
-        a.record()
-        call()
-        b.record()
-    torch.cuda.synchronize()
-    kt = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / iters], device=dev)
+def run_rank_program(exe, args, world, rank, local_rank, tag, key, timeout=120):
+    """Starts one process of a C program of build/bin on this rank's GPU (RANK / WORLD_SIZE / LOCAL_RANK in its
+    environment); the processes of one run meet through a file whose name carries a per-run nonce chosen by rank 0,
+    so that a file left behind by a crashed or killed earlier run (or another job on the machine) is never picked
+    up.  Rank 0 returns the object under `key` of the program's JSON line, the other ranks None."""
+    import tempfile
+    if not exe.exists():
+        return None
+    env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local_rank))
+    nonce = [f"{os.getpid()}_{time.time_ns()}"]
     if world > 1:
-        torch.distributed.all_reduce(kt, op=torch.distributed.ReduceOp.MAX)
-    kern_ms = float(kt[0])
-    seq_ms = timed(opt, gather=True)
-    shard = opt.shard
-    del opt
-    opt = sh.ShardedAdamEMA(p.clone(), chunks=chunks if world > 1 else 1, **kw)
-    tot_ms = timed(opt, gather=True)
-    return {"params": npar, "shard": shard, "kernel_ms": round(kern_ms, 4),
-            "kernel_GBps_per_gpu": round(36 * shard / (kern_ms * 1e-3) / 1e9, 1),
-            "update_then_allgather_ms": round(seq_ms, 4), "update_plus_allgather_ms": round(tot_ms, 4),
-            "chunks": chunks if world > 1 else 1,
-            "allgather_GBps_per_gpu_in": round((world - 1) * shard * 4 / max((seq_ms - kern_ms) * 1e-3, 1e-9) / 1e9, 1)
-            if world > 1 else None}
+        torch.distributed.broadcast_object_list(nonce, src=0)
+    id_file = os.path.join(tempfile.gettempdir(), f"{tag}_{nonce[0]}.ncclid")
+    try:
+        res = subprocess.run([str(exe), *args, "--id-file", id_file], env=env, capture_output=True, text=True,
+                             timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"error": "timeout"} if rank == 0 else None
+    finally:
+        if rank == 0 and os.path.exists(id_file):
+            os.unlink(id_file)
+    if rank != 0:
+        return None
+    if res.returncode != 0:
+        return {"error": (res.stderr or res.stdout)[-300:]}
+    for ln in res.stdout.splitlines():
+        if ln.startswith("{"):
+            return json.loads(ln)[key]
+    return {"error": "no result line"}
+
+
+def sharded_adam_ema(world, rank, local_rank):
+    """Optimizer config: flat 64M-parameter vector, fused Adam+EMA on this rank's range, new parameters published
+    to the other ranks -- csrc/host/sharded_adam_bench.c on csrc/host/b200_sharded_optimizer.c (C, NCCL, CUDA IPC).
+    Three device-timed figures (events around the launches only, max over ranks): the update kernel alone, update
+    then in-place ncclAllGather, and the update whose store phase writes the peers' copies directly."""
+    return run_rank_program(BIN / "sharded_adam_bench", ["--iters", "20", "--warmup", "3"], world, rank, local_rank,
+                            "sharded_adam", "sharded_adam_ema")
 
 
 # ------------------------------------------------------------------------------------ EDM UNet training step
@@ -632,43 +606,22 @@ def edm_train_images_per_s(binary, batch=256, steps=(50, 450), write_config=None
                 "steps_timed": nst, "how": "wall-clock difference of two runs of the unmodified reference trainer"}
 
 
-def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True, fastconv=True):
+def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, graph=True, fastconv=True, sharded=None):
     """Data-parallel EDM UNet training (build/bin/edm_dp_train[_fastconv]: the reference's UNet and host
-    modules, this library's kernels, NCCL gradient all-reduce; `fastconv` links csrc/host/b200_conv2d.c in place of
-    the reference's conv2d.c).  Every rank of this benchmark starts one trainer process on its own GPU; the
-    trainers find each other through a file named after MASTER_PORT.  Rank 0 returns the trainer's JSON
-    (device-timed, max over ranks), the other ranks None."""
-    exe = BIN / ("edm_dp_train_fastconv" if fastconv else "edm_dp_train")
-    if not exe.exists():
-        return None
-    env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local_rank))
-    # the trainers of one run meet through a file; its name carries a per-run nonce chosen by rank 0, so that a
-    # file left behind by a crashed or killed earlier run (or another job on the machine) is never picked up
-    nonce = [f"{os.getpid()}_{time.time_ns()}"]
-    if world > 1:
-        torch.distributed.broadcast_object_list(nonce, src=0)
-    import tempfile
-    id_file = os.path.join(tempfile.gettempdir(), f"edm_dp_train_{nonce[0]}_{batch_per_gpu}_{int(fastconv)}.ncclid")
-    cmd = [str(exe), "--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup), "--id-file", id_file]
+    modules, this library's kernels, NCCL gradient exchange; `fastconv` links csrc/host/b200_conv2d.c in place of
+    the reference's conv2d.c; `sharded` = "allgather" | "peer" selects the range-sharded optimizer).  Every rank of
+    this benchmark starts one trainer process on its own GPU.  Rank 0 returns the trainer's JSON (device-timed,
+    max over ranks), the other ranks None."""
+    args = ["--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup)]
     if graph:
-        cmd.append("--graph")
-    try:
-        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=90)
-    except subprocess.TimeoutExpired:
-        return {"error": "timeout"} if rank == 0 else None
-    finally:
-        if rank == 0 and os.path.exists(id_file):
-            os.unlink(id_file)
-    if rank != 0:
-        return None
-    if res.returncode != 0:
-        return {"error": (res.stderr or res.stdout)[-300:]}
-    for ln in res.stdout.splitlines():
-        if ln.startswith("{"):
-            got = json.loads(ln)["edm_dp_train"]
-            got["conv2d_host_module"] = "csrc/host/b200_conv2d.c" if fastconv else "reference src/conv2d.c"
-            return got
-    return {"error": "no result line"}
+        args.append("--graph")
+    if sharded:
+        args += ["--sharded", sharded]
+    got = run_rank_program(BIN / ("edm_dp_train_fastconv" if fastconv else "edm_dp_train"), args, world, rank,
+                           local_rank, f"edm_dp_train_{batch_per_gpu}_{int(fastconv)}", "edm_dp_train", timeout=90)
+    if isinstance(got, dict) and "error" not in got:
+        got["conv2d_host_module"] = "csrc/host/b200_conv2d.c" if fastconv else "reference src/conv2d.c"
+    return got
 
 
 # ------------------------------------------------------------------------------------ main
@@ -802,7 +755,7 @@ def main():
         del step
         torch.cuda.empty_cache()
         step = None
-        line["sharded_adam_ema"] = sharded_adam_ema(lib, world, rank)
+        line["sharded_adam_ema"] = sharded_adam_ema(world, rank, local)
         # EDM UNet training, images/s: weak scaling (256 per GPU) and strong scaling (256 in total)
         if world > 1:
             torch.distributed.barrier()
@@ -811,6 +764,8 @@ def main():
         if world > 1:
             torch.distributed.barrier()
             dp["strong_256_global"] = edm_dp_train(world, rank, local, 256 // world)
+            torch.distributed.barrier()
+            dp["strong_256_global_sharded_optimizer"] = edm_dp_train(world, rank, local, 256 // world, sharded="peer")
         else:
             dp["weak_256_per_gpu_reference_conv2d"] = edm_dp_train(world, rank, local, 256, fastconv=False)
         line["edm_dp_train"] = dp
@@ -829,9 +784,9 @@ def main():
             # arm once as a plain drop-in at the launch_* ABI and once with the fused residual block linked in
             if not args.no_trainer:
                 if args.impl == "b200":
-                    ddpm = {"drop_in": edm_train_images_per_s(BIN / "ddpm_demo_b200", steps=(20, 120),
+                    ddpm = {"drop_in": edm_train_images_per_s(BIN / "ddpm_demo_b200", steps=(50, 350),
                                                               write_config=write_ddpm_config),
-                            "fused_block": edm_train_images_per_s(BIN / "ddpm_demo_b200_fused", steps=(20, 120),
+                            "fused_block": edm_train_images_per_s(BIN / "ddpm_demo_b200_fused", steps=(50, 350),
                                                                   write_config=write_ddpm_config)}
                 else:
                     ddpm = edm_train_images_per_s(ROOT / "oracle" / "_ref" / "ddpm_demo_ref", steps=(20, 120),

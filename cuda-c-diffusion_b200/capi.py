@@ -78,6 +78,8 @@ SIGNATURES = {
     "launch_film_act_backward": "pppppiiiiis",
     "launch_activation_backward_axpy": "ppppfiis",
     "launch_layernorm_backward_noalloc": "ppppppppiis",
+    "launch_adam_ema_step_bcast": "ppppphffffffffqs",
+    "launch_copy_multi": "his",
     # management
     "b200_set_error_mode": "i",
     "b200_error_count": "",
@@ -122,6 +124,16 @@ class ParamUpdate(ctypes.Structure):
     """B200ParamUpdate of include/b200_layer_kernels.h."""
     _fields_ = [("p", ctypes.c_void_p), ("g", ctypes.c_void_p), ("m", ctypes.c_void_p),
                 ("v", ctypes.c_void_p), ("shadow", ctypes.c_void_p), ("n", ctypes.c_int)]
+
+
+class PeerDests(ctypes.Structure):
+    """B200PeerDests of include/b200_layer_kernels.h."""
+    _fields_ = [("dst", ctypes.c_void_p * 15), ("count", ctypes.c_int)]
+
+
+class CopyItem(ctypes.Structure):
+    """B200CopyItem of include/b200_layer_kernels.h."""
+    _fields_ = [("dst", ctypes.c_void_p), ("src", ctypes.c_void_p), ("n", ctypes.c_int)]
 
 
 class WeightDesc(ctypes.Structure):

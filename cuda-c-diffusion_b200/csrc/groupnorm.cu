@@ -627,6 +627,7 @@ __global__ void __launch_bounds__(GN_THREADS, 2) gn_bwd_tile(const __grid_consta
 }  // namespace b200
 
 #include "groupnorm_strip.cuh"
+#include "groupnorm_dstrip.cuh"
 #include "groupnorm_cstrip.cuh"
 
 namespace b200 {
@@ -935,7 +936,7 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
         return false;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
             (void)cudaGetLastError();
             return false;
         }
@@ -959,8 +960,32 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
     if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
         static bool done[64] = { false };                                                                   \
         return pstrip_launch(gn_bwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, dx, sc.partials,       \
-                   dy, x, gamma, beta, mu, rstd, plan.g, (int)grid)                                         \
-            && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);                           \
+                   dy, x, gamma, beta, mu, rstd, plan.g, (int)grid, fold)                                   \
+            && (fold.rows || (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true));            \
+    }
+
+// deep-staged variants (groupnorm_dstrip.cuh)
+#define DSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
+    if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv) {                                              \
+        static bool done[64] = { false };                                                                   \
+        if (full) {                                                                                         \
+            static bool donef[64] = { false };                                                              \
+            return pstrip_launch(gn_fwd_dstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
+                gamma, beta, plan.g, eps, (int)grid);                                                       \
+        }                                                                                                   \
+        return pstrip_launch(gn_fwd_dstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
+            gamma, beta, plan.g, eps, (int)grid);                                                           \
+    }
+#define DSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
+    if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
+        static bool done[64] = { false };                                                                   \
+        static bool donef[64] = { false };                                                                  \
+        const bool ok = full                                                                                \
+            ? pstrip_launch(gn_bwd_dstrip<NTv, VPTv, ACT, true>, donef, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
+                  gamma, beta, mu, rstd, plan.g, (int)grid, fold)                                           \
+            : pstrip_launch(gn_bwd_dstrip<NTv, VPTv, ACT, false>, done, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
+                  gamma, beta, mu, rstd, plan.g, (int)grid, fold);                                          \
+        return ok && (fold.rows || (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true));      \
     }
 
 #define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
@@ -969,9 +994,9 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
             beta, plan.g, eps);
 #define STRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
-        return strip_launch(gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, plan.smem, s, dx, sc.partials,  \
-                   dy, x, gamma, beta, mu, rstd, plan.g, B)                                                \
-            && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
+        return strip_launch(gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, ssmem, s, dx, sc.partials,      \
+                   dy, x, gamma, beta, mu, rstd, plan.g, B, fold)                                          \
+            && (fold.rows || (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true));
 
 static bool cstrip_plan(StripPlan* out, int HW, int C, int G);
 
@@ -1014,6 +1039,13 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 const long per_cta = (grid + resident - 1) / resident;
                 const long pgrid = (grid + per_cta - 1) / per_cta;
                 const bool full = plan.g.RSTEP * plan.VPT == HW;
+                // deep staging: half a strip more in flight, in the shared memory the plain pipeline leaves unused
+                const size_t dsmem = (size_t)(plan.VPT + plan.VPT / 2) * plan.NT * 16 + plan.smem;
+                // (measured on [256,32,32,256]: 2 % slower than the plain pipeline in forward, so off unless asked for)
+                if (tune_get("gn_deep_fwd", 0) && dsmem * per_sm <= 226 * 1024 && grid >= 3 * pgrid) {
+                    DSTRIP_FWD_CASE(1024, 4, 1) DSTRIP_FWD_CASE(1024, 8, 1)
+                    DSTRIP_FWD_CASE(512, 4, 2) DSTRIP_FWD_CASE(512, 8, 2) DSTRIP_FWD_CASE(512, 8, 1)
+                }
                 PSTRIP_FWD_CASE(1024, 4, 1) PSTRIP_FWD_CASE(1024, 8, 1)
                 PSTRIP_FWD_CASE(512, 4, 2) PSTRIP_FWD_CASE(512, 8, 2) PSTRIP_FWD_CASE(512, 8, 1)
                 PSTRIP_FWD_CASE(256, 4, 4) PSTRIP_FWD_CASE(256, 8, 4)
@@ -1054,8 +1086,16 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
         if (grid > 2147483647L)
             return false;
         Scratch sc;
-        if (!scratch_get(s, (size_t)2 * B * C, 0, &sc))
+        if (!scratch_get(s, (size_t)2 * B * C, 1, &sc))
             return false;
+        // small tables of partial rows are added by the last CTA of the same launch (one ticket per launch)
+        StripFold fold;
+        fold.ticket = sc.tickets;
+        fold.dgamma = dgamma;
+        fold.dbeta = dbeta;
+        fold.rows = ((long)B * 2 * C <= (long)tune_get("gn_inline_fold_floats", 65536) && 2 * C <= 4096) ? B : 0;
+        // the in-kernel fold borrows NT floats of shared memory once the strips are done
+        const size_t ssmem = plan.smem < (size_t)plan.NT * 4 ? (size_t)plan.NT * 4 : plan.smem;
         {
             const int per_sm = (plan.VPT == 8 || plan.NT == 1024) ? 1 : (plan.NT <= 256 ? 2 : 1);
             const long resident = (long)sm_count() * per_sm;
@@ -1064,6 +1104,13 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                 // even share: every CTA gets (almost) the same number of strips
                 const long per_cta = (grid + resident - 1) / resident;
                 const long pgrid = (grid + per_cta - 1) / per_cta;
+                const bool full = plan.g.RSTEP * plan.VPT == HW;
+                const size_t dsmem = (size_t)3 * plan.VPT * plan.NT * 16 + plan.smem;
+                // (2 % faster than the plain pipeline when every CTA walks many strips; with only a few strips per
+                // CTA the longer prologue costs more than the deeper staging gains)
+                if (tune_get("gn_deep", 1) && per_sm == 1 && dsmem <= 226 * 1024 && grid >= 8 * pgrid) {
+                    DSTRIP_BWD_CASE(1024, 4) DSTRIP_BWD_CASE(512, 4) DSTRIP_BWD_CASE(512, 8)
+                }
                 PSTRIP_BWD_CASE(1024, 4, 1) PSTRIP_BWD_CASE(512, 4, 1) PSTRIP_BWD_CASE(512, 8, 1)
                 PSTRIP_BWD_CASE(256, 4, 2)
             }

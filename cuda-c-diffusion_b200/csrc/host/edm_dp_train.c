@@ -30,6 +30,7 @@
  */
 #include "b200_fused_modules.h"
 #include "edm.h" /* reference diffusion/edm.h: only used by --check */
+#include "b200_sharded_optimizer.h"
 
 #include <math.h>
 #include <nccl.h>
@@ -408,6 +409,7 @@ static int env_int(const char* name, int dflt)
 int main(int argc, char** argv)
 {
     int steps = 20, warmup = 5, batch = 256, check = 0, tf32 = 1, log_every = 0, use_graph = 0, batch_wn = 1;
+    int sharded = -1; /* -1: replicated optimizer state; else B200_EXCHANGE_* of the range-sharded optimizer */
     unsigned seed = 410293;
     const char* id_file = "/tmp/edm_dp_train.ncclid";
     const char* dump_path = NULL;
@@ -423,6 +425,15 @@ int main(int argc, char** argv)
         else if (!strcmp(argv[i], "--save") && i + 1 < argc) save_path = argv[++i];
         else if (!strcmp(argv[i], "--resume") && i + 1 < argc) resume_path = argv[++i];
         else if (!strcmp(argv[i], "--check")) check = 1;
+        else if (!strcmp(argv[i], "--sharded") && i + 1 < argc) {
+            const char* how = argv[++i];
+            if (!strcmp(how, "allgather")) sharded = B200_EXCHANGE_ALLGATHER;
+            else if (!strcmp(how, "peer")) sharded = B200_EXCHANGE_PEER_STORE;
+            else {
+                fprintf(stderr, "--sharded takes allgather or peer\n");
+                return 2;
+            }
+        }
         else if (!strcmp(argv[i], "--graph")) use_graph = 1;
         else if (!strcmp(argv[i], "--no-wn-batch")) batch_wn = 0;
         else if (!strcmp(argv[i], "--verbose")) g_verbose = 1;
@@ -476,7 +487,24 @@ int main(int argc, char** argv)
     ema_shadow_list(ema, &shadow_l);
     optimizer_moment_lists(opt, &adam_m, &adam_v);
     int first_step = 1;
-    if (resume_path) {
+    /* --sharded: moments and EMA shadows exist only for this rank's range of the flat parameter vector; the
+       gradient all-reduce becomes a reduce-scatter and the updated range is published to the other ranks */
+    B200ShardedAdam* so = NULL;
+    if (sharded >= 0) {
+        B200ShardedAdamConfig scfg = { .rank = rank, .world = world, .comm = comm, .lr = lr, .beta1 = b1, .beta2 = b2,
+            .eps = eps, .ema_decay = decay, .exchange = sharded, .reduce_grads = 1 };
+        so = b200_sharded_adam_create(&params, &scfg, ctx.stream);
+        if (!so)
+            return 1;
+        if (resume_path) {
+            int loaded_step = 0;
+            if (b200_sharded_adam_load(so, resume_path, &loaded_step, ctx.stream) != 0) {
+                fprintf(stderr, "rank %d: cannot load %s\n", rank, resume_path);
+                return 1;
+            }
+            first_step = loaded_step + 1;
+        }
+    } else if (resume_path) {
         int loaded_step = 0, adam_t = 0;
         if (checkpoint_load_training(resume_path, &loaded_step, &adam_t, &params, &shadow_l, &adam_m, &adam_v) != 0) {
             fprintf(stderr, "rank %d: cannot load %s\n", rank, resume_path);
@@ -556,14 +584,22 @@ int main(int argc, char** argv)
         /* The gradient exchange stays outside the graph: with the grouped all-reduce captured,
            two ranks stopped making progress after the capture step (NCCL 2.27.3), so it is
            issued as one ordinary grouped launch per step. */
-        if (comm) {
-            NCCL_OK(ncclGroupStart());
-            for (int i = 0; i < params.count; ++i)
-                NCCL_OK(ncclAllReduce(params.items[i].grad, params.items[i].grad, (size_t)params.items[i].size,
-                    ncclFloat, ncclSum, comm, ctx.stream));
-            NCCL_OK(ncclGroupEnd());
+        if (so) {
+            b200_sharded_adam_set_lr(so, cur_lr);
+            if (b200_sharded_adam_step(so, ctx.stream) != 0) {
+                fprintf(stderr, "rank %d: sharded optimizer step failed\n", rank);
+                return 1;
+            }
+        } else {
+            if (comm) {
+                NCCL_OK(ncclGroupStart());
+                for (int i = 0; i < params.count; ++i)
+                    NCCL_OK(ncclAllReduce(params.items[i].grad, params.items[i].grad, (size_t)params.items[i].size,
+                        ncclFloat, ncclSum, comm, ctx.stream));
+                NCCL_OK(ncclGroupEnd());
+            }
+            optimizer_ema_step_fused(opt, ema, &params, cur_lr, b1, b2, eps, decay, 1.0f / (float)world, &ctx);
         }
-        optimizer_ema_step_fused(opt, ema, &params, cur_lr, b1, b2, eps, decay, 1.0f / (float)world, &ctx);
         TRACE("rank %d: step %d enqueued\n", rank, step);
         const int logging = step == 1 || step == warmup + steps || (log_every > 0 && step % log_every == 0);
         if (logging && (step <= warmup || step == warmup + steps)) {
@@ -606,12 +642,18 @@ int main(int argc, char** argv)
         printf("{\"edm_dp_train\": {\"images_per_s\": %.1f, \"ms_per_step\": %.3f, \"n_gpus\": %d, \"batch_per_gpu\": %d, "
                "\"steps\": %d, \"warmup\": %d, \"params\": %ld, \"param_tensors\": %d, \"tf32\": %d, "
                "\"library_launches_per_step\": %.1f, \"cuda_graph_nodes\": %zu, \"first_loss\": %.5f, \"last_loss\": %.5f, "
-               "\"replicas_in_sync\": %s, \"b200_device_error\": %d}}\n",
+               "\"replicas_in_sync\": %s, \"b200_device_error\": %d, \"optimizer\": \"%s\"}}\n",
             steps ? (double)batch * world * steps / (h_stat[0] * 1e-3) : 0.0, steps ? h_stat[0] / steps : 0.0, world, batch, steps, warmup, n_params,
             params.count, tf32, steps ? (double)launches_timed / steps : 0.0, graph_nodes, first_loss, last_loss, in_sync ? "true" : "false",
-            b200_device_error_status());
+            b200_device_error_status(),
+            sharded < 0 ? "replicated" : (sharded == B200_EXCHANGE_PEER_STORE ? "range-sharded, peer stores" : "range-sharded, all-gather"));
 
-    if (save_path && rank == 0) {
+    if (save_path && so) { /* every rank takes part in gathering the sharded state; rank 0 writes */
+        if (b200_sharded_adam_save(so, save_path, first_step - 1 + warmup + steps, ctx.stream) != 0) {
+            fprintf(stderr, "cannot write %s\n", save_path);
+            return 1;
+        }
+    } else if (save_path && rank == 0) {
         const int rc = checkpoint_save_training(save_path, first_step - 1 + warmup + steps, optimizer_timestep(opt), &params,
             &shadow_l, &adam_m, &adam_v);
         if (rc != 0) {

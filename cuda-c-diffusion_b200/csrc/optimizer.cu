@@ -88,6 +88,91 @@ __global__ void __launch_bounds__(OPT_THREADS) adam_flat_kernel(float* p, float*
     }
 }
 
+// Fused update of a parameter range whose new values also go to `np` peer copies of the vector.
+// W = 4 only: the sharded optimizer cuts ranges on 16-byte boundaries.
+struct PeerTable {
+    float* dst[B200_MAX_PEERS];
+    int count;
+};
+
+template <bool EMA>
+__global__ void __launch_bounds__(OPT_THREADS) adam_bcast_kernel(float* __restrict__ p, float* __restrict__ m,
+    float* __restrict__ v, float* __restrict__ sh, const float* __restrict__ g, const PeerTable peers, long n,
+    const AdamHyper h, const float bc1)
+{
+    constexpr int U = 2;
+    const long npack = n / 4;
+    const long stride = (long)gridDim.x * OPT_THREADS;
+    for (long i = (long)blockIdx.x * OPT_THREADS + threadIdx.x; i < npack; i += stride * U) {
+        Pack<4> rp[U], rm[U], rv[U], rg[U], rs[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long k = i + u * stride;
+            if (k < npack) {
+                rp[u] = load_stream<4>(p + k * 4);
+                rm[u] = load_stream<4>(m + k * 4);
+                rv[u] = load_stream<4>(v + k * 4);
+                rg[u] = load_stream<4>(g + k * 4);
+                if (EMA)
+                    rs[u] = load_stream<4>(sh + k * 4);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long k = i + u * stride;
+            if (k < npack) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    adam_one<EMA>(rp[u].v[e], rm[u].v[e], rv[u].v[e], rs[u].v[e], rg[u].v[e], h, bc1);
+                const float4 np4 = make_float4(rp[u].v[0], rp[u].v[1], rp[u].v[2], rp[u].v[3]);
+                // the peers first: their stores take the longest to drain
+                for (int d = 0; d < peers.count; ++d)
+                    *reinterpret_cast<float4*>(peers.dst[d] + k * 4) = np4;
+                store_stream<4>(p + k * 4, rp[u]);
+                store_stream<4>(m + k * 4, rm[u]);
+                store_stream<4>(v + k * 4, rv[u]);
+                if (EMA)
+                    store_stream<4>(sh + k * 4, rs[u]);
+            }
+        }
+    }
+}
+
+struct CopyTable {
+    float* dst[B200_MAX_MULTI];
+    const float* src[B200_MAX_MULTI];
+    int n[B200_MAX_MULTI];
+    int block0[B200_MAX_MULTI + 1];
+    int count;
+};
+
+__global__ void __launch_bounds__(OPT_THREADS) copy_multi_kernel(const CopyTable tb)
+{
+    int lo = 0, hi = tb.count - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tb.block0[mid] <= (int)blockIdx.x)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    float* dst = tb.dst[lo];
+    const float* src = tb.src[lo];
+    const int n = tb.n[lo];
+    const int first = (blockIdx.x - tb.block0[lo]) * OPT_THREADS + threadIdx.x;
+    const int stride = (tb.block0[lo + 1] - tb.block0[lo]) * OPT_THREADS;
+    if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0) {
+        const int n4 = n / 4;
+        for (int i = first; i < n4; i += stride)
+            reinterpret_cast<float4*>(dst)[i] = __ldg(reinterpret_cast<const float4*>(src) + i);
+        for (int i = n4 * 4 + first; i < n; i += stride)
+            dst[i] = src[i];
+    } else {
+        for (int i = first; i < n; i += stride)
+            dst[i] = src[i];
+    }
+}
+
 struct AdamTable {
     float* p[B200_MAX_MULTI];
     const float* g[B200_MAX_MULTI];
@@ -204,6 +289,64 @@ void launch_adam_ema_step(float* p, float* m, float* v, float* shadow, const flo
 {
     B200_REQUIRE(n >= 0, "adam_ema_step: n=%lld", n);
     adam_flat(p, m, v, shadow, g, (long)n, make_hyper(lr, beta1, beta2, eps, bc1, bc2, decay, grad_scale), bc1, s);
+}
+
+void launch_adam_ema_step_bcast(float* p, float* m, float* v, float* shadow, const float* g,
+    const B200PeerDests* peers, float lr, float beta1, float beta2, float eps, float bc1, float bc2, float decay,
+    float grad_scale, long long n, cudaStream_t s)
+{
+    B200_REQUIRE(n >= 0 && n % 4 == 0, "adam_ema_step_bcast: n=%lld must be a multiple of 4", n);
+    B200_REQUIRE(peers && peers->count >= 0 && peers->count <= B200_MAX_PEERS, "adam_ema_step_bcast: bad peer table");
+    bool ok = aligned16(p) && aligned16(m) && aligned16(v) && aligned16(g) && (shadow == nullptr || aligned16(shadow));
+    PeerTable tb;
+    tb.count = peers->count;
+    for (int d = 0; d < peers->count; ++d) {
+        tb.dst[d] = peers->dst[d];
+        ok = ok && peers->dst[d] != nullptr && aligned16(peers->dst[d]);
+    }
+    B200_REQUIRE(ok, "adam_ema_step_bcast: every pointer must be 16-byte aligned (and no destination NULL)");
+    if (n == 0)
+        return;
+    const AdamHyper h = make_hyper(lr, beta1, beta2, eps, bc1, bc2, decay, grad_scale);
+    long grid = (n / 4 + OPT_THREADS * 2 - 1) / (OPT_THREADS * 2);
+    const long cap = (long)sm_count() * tune_get("adam_blocks_per_sm", 16);
+    if (grid > cap)
+        grid = cap;
+    if (shadow)
+        adam_bcast_kernel<true><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, shadow, g, tb, (long)n, h, bc1);
+    else
+        adam_bcast_kernel<false><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, shadow, g, tb, (long)n, h, bc1);
+    count_launch();
+    B200_CHECK_LAUNCH();
+}
+
+void launch_copy_multi(const B200CopyItem* items, int count, cudaStream_t s)
+{
+    B200_REQUIRE(count >= 0 && (count == 0 || items), "copy_multi: count=%d", count);
+    const int per_tensor_cap = sm_count() * 4;
+    int i = 0;
+    while (i < count) {
+        CopyTable tb;
+        tb.count = 0;
+        tb.block0[0] = 0;
+        while (i < count && tb.count < B200_MAX_MULTI) {
+            const B200CopyItem& it = items[i++];
+            B200_REQUIRE(it.n >= 0, "copy_multi: item %d has n=%d", i - 1, it.n);
+            if (it.n == 0)
+                continue;
+            const int k = tb.count++;
+            tb.dst[k] = it.dst; tb.src[k] = it.src; tb.n[k] = it.n;
+            int nb = (it.n + OPT_MULTI_ELEMS_PER_BLOCK - 1) / OPT_MULTI_ELEMS_PER_BLOCK;
+            if (nb > per_tensor_cap)
+                nb = per_tensor_cap;
+            tb.block0[k + 1] = tb.block0[k] + nb;
+        }
+        if (tb.count == 0)
+            break;
+        copy_multi_kernel<<<tb.block0[tb.count], OPT_THREADS, 0, s>>>(tb);
+        count_launch();
+        B200_CHECK_LAUNCH();
+    }
 }
 
 void launch_adam_ema_step_multi(const B200ParamUpdate* items, int count, float lr, float beta1, float beta2,

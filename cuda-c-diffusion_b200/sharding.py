@@ -10,8 +10,7 @@ What shards and how (no kernel reads another GPU's memory):
   data-parallel training this rides with the gradient all-reduce.
 * Adam + EMA: sharded by parameter range (`param_range`, 16-byte aligned cuts).
   m, v and the EMA shadow exist only for the local range; after the fused update
-  the new parameters are all-gathered in place (`ShardedAdamEMA`); with `chunks` > 1 the
-  ownership is interleaved so that the gather of one chunk overlaps the update of the next.
+  the new parameters are all-gathered in place (`ShardedAdamEMA`).
 * data-parallel training step: gradients are summed across ranks
   (`allreduce_gradients`) and the 1/world factor is folded into the update's
   `grad_scale`, so no separate scaling pass runs.
@@ -95,59 +94,36 @@ class AdamHyper:
 class ShardedAdamEMA:
     """Fused Adam + EMA over a flat fp32 parameter vector sharded by parameter range.
 
-    Every rank keeps the full (padded) parameter vector, but moments and the EMA
-    shadow only for the elements it owns.  With `chunks` = 1 a rank owns one
-    contiguous range; `step` updates it with one fused pass and all-gathers the new
-    parameters in place (send buffer = own slice of the receive buffer).
+    Every rank keeps the full (padded) parameter vector, but moments and the EMA shadow only
+    for the contiguous range it owns.  `step` updates that range with one fused pass and
+    all-gathers the new parameters in place (send buffer = own slice of the receive buffer).
+    Bias corrections follow the reference host code (optimizer.c:62-64: bc = 1 - beta^t in fp32).
 
-    With `chunks` = K > 1 the vector is cut into K super-chunks and EACH super-chunk
-    is range-sharded over the ranks, so rank r owns piece r of every super-chunk.
-    `step` then updates piece after piece and starts the in-place all-gather of a
-    super-chunk as soon as its piece is done: the exchange of super-chunk i runs on
-    the collective's stream while the update kernel of piece i+1 runs, and every
-    gather is still contiguous.  Bias corrections follow the reference host code
-    (optimizer.c:62-64: bc = 1 - beta^t in fp32).
+    This is the torch.distributed form used by the CPU (gloo) tests of the partitioning; the
+    product form for one process per GPU is csrc/host/b200_sharded_optimizer.c (C, NCCL, with
+    the exchange optionally fused into the update kernel as peer stores).
     """
 
     def __init__(self, params: torch.Tensor, lr, beta1=0.9, beta2=0.999, eps=1e-8, decay=0.999, group=None,
-                 update_fn=None, chunks: int = 1):
-        assert params.dim() == 1 and params.dtype == torch.float32 and chunks >= 1
+                 update_fn=None):
+        assert params.dim() == 1 and params.dtype == torch.float32
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.n = params.numel()
-        self.chunks = chunks
-        # piece: what one rank owns of one super-chunk; all pieces have the same, 16-byte aligned length
-        self.piece = equal_param_range(self.n, self.world * chunks)
-        self.super = self.piece * self.world
-        self.shard = self.piece * chunks  # elements owned by a rank
-        padded = self.super * chunks
+        self.shard = equal_param_range(self.n, self.world)  # 16-byte aligned, the same on every rank
+        padded = self.shard * self.world
         self.params = params if padded == self.n else torch.cat(
             [params, torch.zeros(padded - self.n, dtype=params.dtype, device=params.device)])
+        self.lo, self.hi = self.rank * self.shard, (self.rank + 1) * self.shard
         self.m = torch.zeros(self.shard, dtype=torch.float32, device=params.device)
         self.v = torch.zeros_like(self.m)
-        self.shadow = torch.cat([self.params[lo:hi] for lo, hi in self.owned_ranges()]).clone()
+        self.shadow = self.params[self.lo:self.hi].clone()
         self.lr, self.beta1, self.beta2, self.eps, self.decay = lr, beta1, beta2, eps, decay
         self.t = 0
         self.update_fn = update_fn or _cuda_update
-        self._pending = []
-
-    def owned_ranges(self):
-        """[(lo, hi)] of the padded parameter vector owned by this rank, one range per super-chunk."""
-        return [(i * self.super + self.rank * self.piece, i * self.super + (self.rank + 1) * self.piece)
-                for i in range(self.chunks)]
-
-    # contiguous ownership (chunks == 1) keeps the earlier attribute names
-    @property
-    def lo(self):
-        return self.owned_ranges()[0][0]
-
-    @property
-    def hi(self):
-        return self.owned_ranges()[0][1]
 
     def local_params(self) -> torch.Tensor:
-        assert self.chunks == 1, "local_params is a single view only for contiguous ownership"
         return self.params[self.lo:self.hi]
 
     def hyper(self, grad_scale=1.0) -> AdamHyper:
@@ -163,34 +139,16 @@ class ShardedAdamEMA:
         return g.contiguous()
 
     def step(self, grads: torch.Tensor, grad_scale: float = 1.0, gather: bool = True) -> None:
-        """`grads`: full (padded or unpadded) flat gradient; only the owned ranges are read."""
+        """`grads`: full (padded or unpadded) flat gradient; only the owned range is read."""
         self.t += 1
-        hyper = self.hyper(grad_scale)
-        overlap = gather and self.world > 1 and self.chunks > 1
-        for i, (lo, hi) in enumerate(self.owned_ranges()):
-            sl = slice(i * self.piece, (i + 1) * self.piece)
-            self.update_fn(self.params[lo:hi], self.m[sl], self.v[sl], self.shadow[sl], self._grad_piece(grads, lo, hi),
-                           hyper)
-            if overlap:  # exchange super-chunk i while the next piece is being updated
-                self._pending.append(dist.all_gather_into_tensor(
-                    self.params[i * self.super:(i + 1) * self.super], self.params[lo:hi], group=self.group,
-                    async_op=True))
-        if overlap:
-            self.wait()
-        elif gather:
+        self.update_fn(self.local_params(), self.m, self.v, self.shadow, self._grad_piece(grads, self.lo, self.hi),
+                       self.hyper(grad_scale))
+        if gather:
             self.all_gather()
-
-    def wait(self) -> None:
-        """Makes the current stream (or the host, for CPU backends) wait for the exchanges in flight."""
-        for w in self._pending:
-            w.wait()
-        self._pending = []
 
     def all_gather(self) -> None:
         if self.world > 1:
-            for i, (lo, hi) in enumerate(self.owned_ranges()):
-                dist.all_gather_into_tensor(self.params[i * self.super:(i + 1) * self.super], self.params[lo:hi],
-                                            group=self.group)
+            dist.all_gather_into_tensor(self.params, self.local_params(), group=self.group)
 
     def full_params(self) -> torch.Tensor:
         return self.params[:self.n]
@@ -199,13 +157,10 @@ class ShardedAdamEMA:
         """Moments and shadow gathered to the unsharded layout (what a checkpoint stores per tensor)."""
         outs = []
         for t in (self.m, self.v, self.shadow):
-            full = torch.empty(self.super * self.chunks, dtype=t.dtype, device=t.device)
-            for i in range(self.chunks):
-                piece = t[i * self.piece:(i + 1) * self.piece].contiguous()
-                dst = full[i * self.super:(i + 1) * self.super]
-                if self.world > 1:
-                    dist.all_gather_into_tensor(dst, piece, group=self.group)
-                else:
-                    dst.copy_(piece)
+            full = torch.empty(self.shard * self.world, dtype=t.dtype, device=t.device)
+            if self.world > 1:
+                dist.all_gather_into_tensor(full, t.contiguous(), group=self.group)
+            else:
+                full.copy_(t)
             outs.append(full[:self.n])
         return tuple(outs)

@@ -257,6 +257,32 @@ void launch_col2im_assign(float* grad_im, const float* grad_col, int batch, int 
 void launch_axpby_rows(float* out, const float* a, const float* b, const float* wa,
     const float* wb, int rows, int dim, cudaStream_t s);
 
+/* Fused Adam+EMA on a parameter range that ALSO writes the new parameters into up to B200_MAX_PEERS further
+   buffers: the range-sharded optimizer's update and its all-gather in one kernel.  Each dst[k] is the address
+   of the same range inside another GPU's copy of the parameter vector (a peer pointer obtained through CUDA
+   IPC or any other peer mapping; plain 128-bit stores over NVLink, no multicast, no TMA), so the exchange
+   happens in the update's store phase instead of a separate collective.  Everything else as
+   launch_adam_ema_step.  p, m, v, shadow, g and every dst must be 16-byte aligned and n a multiple of 4
+   (range cuts of the sharded optimizer are).  The kernel only stores to the peers: ordering against the
+   peers' readers is the caller's (a collective or an event exchange after the launch). */
+#define B200_MAX_PEERS 15
+typedef struct {
+    float* dst[B200_MAX_PEERS];
+    int count;
+} B200PeerDests;
+void launch_adam_ema_step_bcast(float* p, float* m, float* v, float* shadow, const float* g,
+    const B200PeerDests* peers, float lr, float beta1, float beta2, float eps, float bc1, float bc2, float decay,
+    float grad_scale, long long n, cudaStream_t s);
+
+/* dst_i[0:n_i] = src_i[0:n_i] for a table of up to B200_MAX_MULTI ranges per launch: packs the gradients of a
+   ParamList into a flat arena (and unpacks the parameters) for the range-sharded optimizer in one launch. */
+typedef struct {
+    float* dst;
+    const float* src;
+    int n;
+} B200CopyItem;
+void launch_copy_multi(const B200CopyItem* items, int count, cudaStream_t s);
+
 /* LayerNorm backward that allocates nothing.  It has no counterpart in the reference.
    For hosts that run under a fixed device-memory plan and may not enter the CUDA allocator
    after set-up (boards whose heap is sized once by the module constructors, or call sites

@@ -19,7 +19,7 @@ def _code(arg):
         return ""
     if "cudaStream_t" in arg:
         return "s"
-    if "B200ParamUpdate" in arg or "B200WeightDesc" in arg or "B200WeightGradDesc" in arg or "char*" in arg:
+    if any(k in arg for k in ("B200ParamUpdate", "B200WeightDesc", "B200WeightGradDesc", "B200PeerDests", "B200CopyItem", "char*")):
         return "h"
     if "*" in arg:
         return "p"
