@@ -647,7 +647,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-trainer", action="store_true", help="skip the EDM trainer legs (profiler captures)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=INT",
-                    help="set a kernel tunable (b200_tune_set), e.g. gn_no_strip=1 to time the TMA tile kernels")
+                    help="set a kernel tunable (b200_tune_set), e.g. gn_deep=0 to time the backward strips without the deeper staging")
     ap.add_argument("--batch", type=int, default=256, help="samples per GPU; values other than 256 are for profiling only")
     ap.add_argument("--write-edm-config", metavar="FOLDER", help="write images.bin + edm_<steps>.ini for the reference's "
                     "EDM trainer (same config as the timing leg) and exit")

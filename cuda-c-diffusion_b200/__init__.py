@@ -2,13 +2,14 @@
 
 The product is `libb200_layer_kernels.so` (sources in `csrc/`, header in
 `include/b200_layer_kernels.h`).  This package only builds it (`build.py`),
-binds it (`capi.py`) and offers tensor-level wrappers (`ops.py`), the host-side
-mirror of the reference's Module interface (`modules.py`) and the multi-GPU
-sharding helpers (`sharding.py`).
+binds it (`capi.py`) and offers tensor-level wrappers (`ops.py`) and the torch.distributed
+form of the multi-GPU partitioning (`sharding.py`).  The host side proper is C: the reference's own
+modules linked against the library, plus `csrc/host/` (fused modules, replaced residual blocks and
+conv2d, data-parallel trainer, range-sharded optimizer).
 
 The directory name contains a hyphen, so import it with
 `importlib.import_module("cuda-c-diffusion_b200")`.
 """
 from . import capi  # noqa: F401
 
-__all__ = ["capi", "build", "ops", "modules", "sharding"]
+__all__ = ["capi", "build", "ops", "sharding"]

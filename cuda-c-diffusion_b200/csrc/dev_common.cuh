@@ -353,80 +353,21 @@ __device__ __forceinline__ f32x2 act_slope_x2(f32x2 z)
     }
 }
 
-// --- mbarrier / bulk tensor copy (TMA) primitives ----------------------------
+// shared-memory address of a generic pointer (operand of cp.async)
 __device__ __forceinline__ uint32_t smem_addr(const void* p)
 {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count)
+// one butterfly step of a warp reduction on four lanes of data at once
+__device__ __forceinline__ float4 shfl_xor4(float4 v, int off)
 {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+    v.z += __shfl_xor_sync(0xffffffffu, v.z, off);
+    v.w += __shfl_xor_sync(0xffffffffu, v.w, off);
+    return v;
 }
-
-__device__ __forceinline__ void mbar_init_fence()
-{
-    // make the initialised barriers visible to the async (TMA) proxy
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity)
-{
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait: gives up after ~2^22 polls (seconds at the very most), records
-// the failure in the library's device error word (`err`) and returns false so
-// the caller can unwind.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* err)
-{
-    for (unsigned it = 0; it < (1u << 22); ++it) {
-        if (mbar_try_wait(bar, parity))
-            return true;
-        if (it > 64)
-            __nanosleep(64);
-    }
-    atomicExch(err, 1);
-    return false;
-}
-
-// 2-D tile, global -> this CTA's shared memory, completion counted on `bar`.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int x, int y, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_addr(smem_dst)), "l"(tmap), "r"(smem_addr(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-// 2-D tile, shared -> global, tracked by the bulk async-group of this thread.
-__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
-        ::"l"(tmap), "r"(smem_addr(smem_src)), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all committed stores have finished READING shared memory
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// generic-proxy writes to shared memory become visible to the async proxy
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 #endif  // __CUDACC__
 

@@ -175,7 +175,7 @@ template <int NT, int VPT, int ACT, bool FULL>
 __global__ void __launch_bounds__(NT, 1) gn_bwd_dstrip(float* __restrict__ dx, float* __restrict__ partials,
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
-    const int nitems, const StripFold fold)
+    const int nitems)
 {
     extern __shared__ float4 strip_stage[];
     constexpr int NW = NT / 32;
@@ -324,7 +324,6 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_dstrip(float* __restrict__ dx, f
         }
     }
     cp_async_wait_all();
-    strip_ticket_fold<NT>(fold, partials, g.C, reinterpret_cast<float*>(xs));
 }
 
 }  // namespace b200

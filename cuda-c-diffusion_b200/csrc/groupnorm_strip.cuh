@@ -22,7 +22,7 @@
 // result deterministic and keeps fences and atomics off each strip's critical path.
 //
 // The strip must fit the register file: HW <= RSTEP * VPT with VPT <= 8 per
-// tensor.  Larger samples take the TMA / cluster tile kernels of groupnorm.cu.
+// tensor.  Taller samples take the chunked strips of groupnorm_cstrip.cuh.
 #pragma once
 
 namespace b200 {
@@ -85,61 +85,6 @@ struct StripGeom {
     // sharing an SM run out of phase (one loads while the other computes and stores)
     int stagger_lo, stagger_hi, stagger_ns;
 };
-
-// Optional tail of the backward kernels: the last CTA to finish adds the per-sample partial rows
-// itself, which saves the separate fold launch when the table is small (a launch costs more than
-// reading a few tens of KB from L2).  One ticket per LAUNCH, taken after a CTA's last strip, so it
-// is off every strip's critical path.  Fixed summation order: row lanes ascending, then lanes
-// ascending.  `stage_floats` is shared memory no longer in use, at least NT floats.
-struct StripFold {
-    unsigned int* ticket;  // zero on entry, zero again on exit
-    float* dgamma;
-    float* dbeta;
-    int rows;              // partial rows to add (0 = leave the partials to the fold kernel)
-};
-
-template <int NT>
-__device__ __forceinline__ void strip_ticket_fold(const StripFold f, const float* __restrict__ partials, int C,
-    float* stage_floats)
-{
-    if (f.rows <= 0)
-        return;
-    __shared__ unsigned int is_last;
-    __threadfence();  // this CTA's partial rows are visible before its ticket is
-    __syncthreads();
-    if (threadIdx.x == 0)
-        is_last = atomicAdd(f.ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
-    __syncthreads();
-    if (!is_last)
-        return;
-    __threadfence();
-    const int cols = 2 * C;
-    const int lanes = cols >= NT ? 1 : NT / cols;
-    for (int c0 = 0; c0 < cols; c0 += NT) {
-        const int col = c0 + (int)threadIdx.x % (lanes == 1 ? NT : cols);
-        const int lane = lanes == 1 ? 0 : (int)threadIdx.x / cols;
-        float acc = 0.0f;
-        if (col < cols && lane < lanes)
-            for (int r = lane; r < f.rows; r += lanes)
-                acc += __ldcg(partials + (size_t)r * cols + col);
-        if (lanes == 1) {
-            if (col < cols)
-                (col < C ? f.dgamma[col] : f.dbeta[col - C]) = acc;
-        } else {
-            stage_floats[threadIdx.x] = acc;
-            __syncthreads();
-            if ((int)threadIdx.x < cols) {
-                float s = 0.0f;
-                for (int l = 0; l < lanes; ++l)
-                    s += stage_floats[l * cols + threadIdx.x];
-                ((int)threadIdx.x < C ? f.dgamma[threadIdx.x] : f.dbeta[threadIdx.x - C]) = s;
-            }
-            __syncthreads();
-        }
-    }
-    if (threadIdx.x == 0)
-        *f.ticket = 0u;
-}
 
 // ---------------------------------------------------------------------------
 // forward: grid = B * nct, block = NT
@@ -231,14 +176,17 @@ __global__ void __launch_bounds__(NT, (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))) gn_
 // backward: grid = B * nct, block = NT
 // Per-sample partial rows of the parameter gradients go to partials[b][2*C] (first C: dgamma,
 // next C: dbeta); a small fold kernel launched right after adds the B rows in a fixed order.
-// (A last-CTA ticket inside this kernel was measured: its fence + atomic round trip sits on
-// every strip's critical path and costs far more than the extra 4-7 us launch.)
+// (A last-CTA ticket inside this kernel was measured twice.  Per strip: its fence + atomic round
+// trip sits on every strip's critical path and costs far more than the extra launch.  Per launch,
+// with the last CTA adding the rows itself: one CTA walking a 128 x 128 table is a chain of L2
+// round trips, [128,28,28,64] went from 19 us to 30 us, and the extra code slowed the strip loop
+// of the large shapes by 10 %.  The separate fold kernel, spread over 4-16 CTAs, stays.)
 // ---------------------------------------------------------------------------
 template <int NT, int VPT, int ACT, int MB>
 __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
     float* __restrict__ partials, const float* __restrict__ dy, const float* __restrict__ x,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mu,
-    const float* __restrict__ rstd, const StripGeom g, const int B, const StripFold fold)
+    const float* __restrict__ rstd, const StripGeom g, const int B)
 {
     extern __shared__ float strip_smem[];
     constexpr int NW = NT / 32;
@@ -337,7 +285,6 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
             __stcs(reinterpret_cast<float4*>(dx + base + (size_t)r * g.C), o);
         }
     }
-    strip_ticket_fold<NT>(fold, partials, g.C, red);
 }
 
 // ===========================================================================
@@ -495,7 +442,7 @@ template <int NT, int VPT, int ACT, int MB>
 __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, float* __restrict__ partials,
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
-    const int nitems, const StripFold fold)
+    const int nitems)
 {
     extern __shared__ float4 strip_stage[];
     constexpr int NW = NT / 32;
@@ -610,7 +557,6 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
             ++b;
         }
     }
-    strip_ticket_fold<NT>(fold, partials, g.C, reinterpret_cast<float*>(stage));
 }
 
 }  // namespace b200

@@ -1,7 +1,7 @@
 /* Host-side C modules for the additive fused entry points of libb200_layer_kernels.so.
  *
- * These are the pieces a maintainer of the reference adds to its tree to use the fusions
- * (see INTEGRATION.md): they implement the reference's own `Module` vtable (src/nn.h:159-174)
+ * These are the pieces a maintainer of the reference adds to its tree to use the fusions:
+ * they implement the reference's own `Module` vtable (src/nn.h:159-174)
  * and use only its public optimizer / EMA API (src/nn.h:216-254).  The file is compiled with
  * the reference's `src/` on the include path; it needs `nn.h` and is NOT self-contained.
  */

@@ -6,9 +6,9 @@ Same names, argument order and behaviour as the C vtable (src/nn.h:159-174):
                                                           gradients are overwritten
     parameters(pl)                                     -- appends (param, grad, size)
     free()
-and the constructors of src/nn.h:185-198, 273-283.  The production host side is the
-reference's own C modules linked against the library; this mirror exists so that tests,
-the benchmark and the multi-GPU plumbing can drive the same call sequences from Python.
+and the constructors of src/nn.h:185-198, 273-283.  TEST SCAFFOLDING: the production host side is the
+reference's own C modules linked against the library (and csrc/host/*.c); this mirror exists so that
+tests/test_modules_gpu.py can drive the same call sequences from Python.
 All compute goes through the C ABI; dense products (mp_linear) go to cuBLAS via torch.matmul
 exactly as the reference sends them to cublasSgemm.
 """
@@ -19,7 +19,9 @@ from dataclasses import dataclass, field
 
 import torch
 
-from . import ops
+import importlib
+
+ops = importlib.import_module("cuda-c-diffusion_b200.ops")
 
 
 @dataclass

