@@ -89,6 +89,39 @@ int* device_error_word();
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Every kernel of the library is launched through launch_k.  With programmatic dependent launch on
+// (tunable "pdl", default 1) a kernel may be scheduled while the kernel before it on the stream is
+// still draining: its CTAs take the SMs that fall free during the predecessor's last wave and stop at
+// pdl_prologue() until the predecessor has completed and its writes are visible.  That removes the
+// launch gap (1.5-3 us) between back-to-back kernels of this library, which is most of the run time
+// of the small layers of a training step.  A predecessor that is not one of these kernels (cuBLAS, a
+// copy) simply completes first, as in an ordinary launch; inside stream capture the dependency
+// becomes a programmatic edge of the graph.
+inline void pdl_attribute(cudaLaunchAttribute* at, unsigned* n)
+{
+    if (tune_get("pdl", 1)) {
+        at[*n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[*n].val.programmaticStreamSerializationAllowed = 1;
+        ++*n;
+    }
+}
+
+template <class... KArgs, class... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    unsigned n = 0;
+    pdl_attribute(at, &n);
+    cfg.attrs = at;
+    cfg.numAttrs = n;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in B200_CHECK_LAUNCH
+}
+
 // ---------------------------------------------------------------------------
 // device side
 // ---------------------------------------------------------------------------
@@ -351,6 +384,14 @@ __device__ __forceinline__ f32x2 act_slope_x2(f32x2 z)
         unpk(z, z0, z1);
         return pk(act_slope<ACT>(z0), act_slope<ACT>(z1));
     }
+}
+
+// First statement of every kernel: wait until the kernels this launch depends on have completed
+// and flushed (a no-op for an ordinary launch), then let the next kernel on the stream be scheduled.
+__device__ __forceinline__ void pdl_prologue()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // shared-memory address of a generic pointer (operand of cp.async)

@@ -25,6 +25,7 @@ constexpr int EW_THREADS = 256;
 template <int W, int U, class Op>
 __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const Op op, const long n)
 {
+    pdl_prologue();
     const long npack = n / W;
     const long stride = (long)gridDim.x * (EW_THREADS * U);
     for (long i = (long)blockIdx.x * (EW_THREADS * U) + threadIdx.x; i < npack; i += stride) {
@@ -71,13 +72,13 @@ static void ew_launch(const Op& op, long n, bool vec_ok, cudaStream_t s)
     if (vec_ok) {
         const long npack = n / 4;
         if (U >= 8)
-            ew_kernel<4, 8, Op><<<ew_grid(npack, 8), EW_THREADS, 0, s>>>(op, n);
+            launch_k(ew_kernel<4, 8, Op>, ew_grid(npack, 8), EW_THREADS, 0, s, op, n);
         else if (U >= 4)
-            ew_kernel<4, 4, Op><<<ew_grid(npack, 4), EW_THREADS, 0, s>>>(op, n);
+            launch_k(ew_kernel<4, 4, Op>, ew_grid(npack, 4), EW_THREADS, 0, s, op, n);
         else
-            ew_kernel<4, 2, Op><<<ew_grid(npack, 2), EW_THREADS, 0, s>>>(op, n);
+            launch_k(ew_kernel<4, 2, Op>, ew_grid(npack, 2), EW_THREADS, 0, s, op, n);
     } else {
-        ew_kernel<1, 4, Op><<<ew_grid(n, 4), EW_THREADS, 0, s>>>(op, n);
+        launch_k(ew_kernel<1, 4, Op>, ew_grid(n, 4), EW_THREADS, 0, s, op, n);
     }
     count_launch();
     B200_CHECK_LAUNCH();
@@ -436,6 +437,7 @@ __global__ void __launch_bounds__(256) film_act_backward_kernel(float* __restric
     const float* __restrict__ grad_out, const float* __restrict__ in, const float* __restrict__ cond, int HW, int C,
     int rows_per_split)
 {
+    pdl_prologue();
     __shared__ float part[8][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     const int b = blockIdx.y;
@@ -465,6 +467,7 @@ __global__ void __launch_bounds__(256) film_act_backward_kernel(float* __restric
 
 __global__ void film_fold_splits_kernel(float* __restrict__ out, const float* __restrict__ partial, int n, int splits)
 {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float t = 0.0f;
@@ -561,13 +564,13 @@ static void film_act_backward_launch(float* grad_in, float* grad_cond, const flo
         }
         sums = sc.partials;
     }
-    film_act_backward_kernel<ACT><<<dim3((C + 31) / 32, batch, splits), dim3(32, 8), 0, s>>>(grad_in, sums, grad_out, in,
+    launch_k(film_act_backward_kernel<ACT>, dim3((C + 31) / 32, batch, splits), dim3(32, 8), 0, s, grad_in, sums, grad_out, in,
         cond, HW, C, rows_per_split);
     count_launch();
     B200_CHECK_LAUNCH();
     if (splits > 1) {
         const int n = batch * C;
-        film_fold_splits_kernel<<<(n + 255) / 256, 256, 0, s>>>(grad_cond, sums, n, splits);
+        launch_k(film_fold_splits_kernel, (n + 255) / 256, 256, 0, s, grad_cond, sums, n, splits);
         count_launch();
         B200_CHECK_LAUNCH();
     }

@@ -15,6 +15,7 @@ namespace b200 {
 __global__ void __launch_bounds__(256) mp_fourier_kernel(float* __restrict__ out, const float* __restrict__ x,
     const float* __restrict__ freqs, const float* __restrict__ phases, int total, int C)
 {
+    pdl_prologue();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int b = i / C, k = i - b * C;
         out[i] = 1.41421356237f * cosf(6.28318530718f * (__ldg(x + b) * __ldg(freqs + k) + __ldg(phases + k)));
@@ -25,6 +26,7 @@ __global__ void __launch_bounds__(256) mp_fourier_kernel(float* __restrict__ out
 __global__ void __launch_bounds__(256) sinusoidal_kernel(float* __restrict__ out, const float* __restrict__ t,
     int batch, int C, float log_max_period)
 {
+    pdl_prologue();
     const int half = C / 2;
     const int total = batch * half;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -47,6 +49,7 @@ __device__ __forceinline__ int table_row(float f, int T)
 __global__ void __launch_bounds__(256) embed_gather_kernel(float* __restrict__ out, const float* __restrict__ table,
     const float* __restrict__ idx, int total, int C, int T)
 {
+    pdl_prologue();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int b = i / C, c = i - b * C;
         out[i] = __ldg(table + (size_t)table_row(__ldg(idx + b), T) * C + c);
@@ -56,6 +59,7 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(float* __restrict__ o
 __global__ void __launch_bounds__(256) embed_scatter_kernel(float* __restrict__ grad_table,
     const float* __restrict__ grad_out, const float* __restrict__ idx, int total, int C, int T)
 {
+    pdl_prologue();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int b = i / C, c = i - b * C;
         atomicAdd(grad_table + (size_t)table_row(__ldg(idx + b), T) * C + c, grad_out[i]);
@@ -83,7 +87,7 @@ void launch_mp_fourier(float* out, const float* x, const float* freqs, const flo
     B200_REQUIRE(batch >= 0 && C > 0 && (long)batch * C < 2147483648L, "mp_fourier: batch=%d C=%d", batch, C);
     if (batch == 0)
         return;
-    mp_fourier_kernel<<<small_grid((long)batch * C), 256, 0, s>>>(out, x, freqs, phases, batch * C, C);
+    launch_k(mp_fourier_kernel, small_grid((long)batch * C), 256, 0, s, out, x, freqs, phases, batch * C, C);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -94,7 +98,7 @@ void launch_sinusoidal(float* out, const float* t, int batch, int C, float log_m
         "sinusoidal: batch=%d C=%d (C must be even)", batch, C);
     if (batch == 0)
         return;
-    sinusoidal_kernel<<<small_grid((long)batch * (C / 2)), 256, 0, s>>>(out, t, batch, C, log_max_period);
+    launch_k(sinusoidal_kernel, small_grid((long)batch * (C / 2)), 256, 0, s, out, t, batch, C, log_max_period);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -105,7 +109,7 @@ void launch_embed_gather(float* out, const float* table, const float* idx, int b
     B200_REQUIRE(batch >= 0 && C > 0 && T > 0 && (long)batch * C < 2147483648L, "embed_gather: bad extents");
     if (batch == 0)
         return;
-    embed_gather_kernel<<<small_grid((long)batch * C), 256, 0, s>>>(out, table, idx, batch * C, C, T);
+    launch_k(embed_gather_kernel, small_grid((long)batch * C), 256, 0, s, out, table, idx, batch * C, C, T);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -116,7 +120,7 @@ void launch_embed_scatter(float* grad_table, const float* grad_out, const float*
     B200_REQUIRE(batch >= 0 && C > 0 && T > 0 && (long)batch * C < 2147483648L, "embed_scatter: bad extents");
     if (batch == 0)
         return;
-    embed_scatter_kernel<<<small_grid((long)batch * C), 256, 0, s>>>(grad_table, grad_out, idx, batch * C, C, T);
+    launch_k(embed_scatter_kernel, small_grid((long)batch * C), 256, 0, s, grad_table, grad_out, idx, batch * C, C, T);
     count_launch();
     B200_CHECK_LAUNCH();
 }

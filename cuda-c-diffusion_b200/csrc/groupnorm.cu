@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(GN_GENERIC_THREADS) gn_fwd_generic(float* __re
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, int HW, int C, int G, float eps)
 {
+    pdl_prologue();
     __shared__ float buf[32];
     const int b = blockIdx.x / G, grp = blockIdx.x % G;
     const int cpg = C / G, n = HW * cpg, cbase = grp * cpg;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(GN_GENERIC_THREADS) gn_bwd_dx_generic(float* _
     const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
     const float* __restrict__ mu, const float* __restrict__ rstd, int HW, int C, int G)
 {
+    pdl_prologue();
     __shared__ float buf[32];
     const int b = blockIdx.x / G, grp = blockIdx.x % G;
     const int cpg = C / G, n = HW * cpg, cbase = grp * cpg;
@@ -116,6 +118,7 @@ __global__ void __launch_bounds__(256) gn_bwd_param_generic(float* __restrict__ 
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, int HW, int C, int G)
 {
+    pdl_prologue();
     __shared__ float sg[8][33], sb[8][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     const int b = blockIdx.y;
@@ -235,6 +238,11 @@ static bool strip_launch(void (*kernel)(KArgs...), long grid, int NT, size_t sme
     cfg.blockDim = dim3((unsigned)NT, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    unsigned nat = 0;
+    pdl_attribute(at, &nat);
+    cfg.attrs = at;
+    cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -543,7 +551,7 @@ static void gn_forward(float* y, float* mu, float* rstd, const float* x, const f
         return;
     if (gn_forward_cstrip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
-    gn_fwd_generic<ACT><<<B * G, GN_GENERIC_THREADS, 0, s>>>(y, mu, rstd, x, gamma, beta, HW, C, G, eps);
+    launch_k(gn_fwd_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, y, mu, rstd, x, gamma, beta, HW, C, G, eps);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -560,10 +568,10 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     Scratch sc;
     B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
     B200_REQUIRE(B <= 65535, "groupnorm_backward: batch %d too large for the generic path", B);
-    gn_bwd_dx_generic<ACT><<<B * G, GN_GENERIC_THREADS, 0, s>>>(dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
+    launch_k(gn_bwd_dx_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
     count_launch();
     B200_CHECK_LAUNCH();
-    gn_bwd_param_generic<ACT><<<dim3((C + 31) / 32, B), dim3(32, 8), 0, s>>>(sc.partials, dy, x, gamma, beta, mu,
+    launch_k(gn_bwd_param_generic<ACT>, dim3((C + 31) / 32, B), dim3(32, 8), 0, s, sc.partials, dy, x, gamma, beta, mu,
         rstd, HW, C, G);
     count_launch();
     B200_CHECK_LAUNCH();

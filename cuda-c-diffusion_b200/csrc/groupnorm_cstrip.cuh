@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems, const int nchunks)
 {
+    pdl_prologue();
     extern __shared__ float4 strip_stage[];
     float4* stage = strip_stage;
     float* red = reinterpret_cast<float*>(stage + VPT * NT);
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_cstrip(float* __restrict__ dx, 
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
     const int nitems, const int nchunks)
 {
+    pdl_prologue();
     extern __shared__ float4 strip_stage[];
     constexpr int NW = NT / 32;
     float4* stage = strip_stage;

@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_dstrip(float* __restrict__ y, f
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
 {
+    pdl_prologue();
     constexpr int HEAD = VPT / 2;
     extern __shared__ float4 strip_stage[];
     float4* head = strip_stage;                   // [2][HEAD][NT]
@@ -177,6 +178,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_dstrip(float* __restrict__ dx, f
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
     const int nitems)
 {
+    pdl_prologue();
     extern __shared__ float4 strip_stage[];
     constexpr int NW = NT / 32;
     float4* xs = strip_stage;              // [2][VPT][NT]

@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(NT, (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))) gn_
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const StripGeom g, const float eps)
 {
+    pdl_prologue();
     extern __shared__ float strip_smem[];
     float* red = strip_smem;
     const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * (NT / 32) * g.Ct : 2 * NT * 4;
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mu,
     const float* __restrict__ rstd, const StripGeom g, const int B)
 {
+    pdl_prologue();
     extern __shared__ float strip_smem[];
     constexpr int NW = NT / 32;
     float* red = strip_smem;
@@ -338,6 +340,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_pstrip(float* __restrict__ y,
     float* __restrict__ mu, float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
 {
+    pdl_prologue();
     extern __shared__ float4 strip_stage[];
     float4* stage = strip_stage;
     float* red = reinterpret_cast<float*>(stage + VPT * NT);
@@ -444,6 +447,7 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_pstrip(float* __restrict__ dx, 
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
     const int nitems)
 {
+    pdl_prologue();
     extern __shared__ float4 strip_stage[];
     constexpr int NW = NT / 32;
     float4* stage = strip_stage;

@@ -76,6 +76,7 @@ template <int W, bool EMA>
 __global__ void __launch_bounds__(OPT_THREADS) adam_flat_kernel(float* p, float* m, float* v, float* sh,
     const float* g, long n, const AdamHyper h, const float bc1)
 {
+    pdl_prologue();
     const long first = (long)blockIdx.x * OPT_THREADS + threadIdx.x;
     const long stride = (long)gridDim.x * OPT_THREADS;
     adam_span<W, EMA>(p, m, v, sh, g, n, h, bc1, first, stride);
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(OPT_THREADS) adam_bcast_kernel(float* __restri
     float* __restrict__ v, float* __restrict__ sh, const float* __restrict__ g, const PeerTable peers, long n,
     const AdamHyper h, const float bc1)
 {
+    pdl_prologue();
     constexpr int U = 2;
     const long npack = n / 4;
     const long stride = (long)gridDim.x * OPT_THREADS;
@@ -148,6 +150,7 @@ struct CopyTable {
 
 __global__ void __launch_bounds__(OPT_THREADS) copy_multi_kernel(const CopyTable tb)
 {
+    pdl_prologue();
     int lo = 0, hi = tb.count - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -188,6 +191,7 @@ constexpr int OPT_MULTI_ELEMS_PER_BLOCK = OPT_THREADS * 4 * 4;  // 4096 floats p
 
 __global__ void __launch_bounds__(OPT_THREADS) adam_multi_kernel(const AdamTable tb, const AdamHyper h, const float bc1)
 {
+    pdl_prologue();
     int lo = 0, hi = tb.count - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -258,14 +262,14 @@ static void adam_flat(float* p, float* m, float* v, float* sh, const float* g, l
         grid = 1;
     if (vec) {
         if (sh)
-            adam_flat_kernel<4, true><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, sh, g, n, h, bc1);
+            launch_k(adam_flat_kernel<4, true>, (int)grid, OPT_THREADS, 0, s, p, m, v, sh, g, n, h, bc1);
         else
-            adam_flat_kernel<4, false><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, sh, g, n, h, bc1);
+            launch_k(adam_flat_kernel<4, false>, (int)grid, OPT_THREADS, 0, s, p, m, v, sh, g, n, h, bc1);
     } else {
         if (sh)
-            adam_flat_kernel<1, true><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, sh, g, n, h, bc1);
+            launch_k(adam_flat_kernel<1, true>, (int)grid, OPT_THREADS, 0, s, p, m, v, sh, g, n, h, bc1);
         else
-            adam_flat_kernel<1, false><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, sh, g, n, h, bc1);
+            launch_k(adam_flat_kernel<1, false>, (int)grid, OPT_THREADS, 0, s, p, m, v, sh, g, n, h, bc1);
     }
     count_launch();
     B200_CHECK_LAUNCH();
@@ -313,9 +317,9 @@ void launch_adam_ema_step_bcast(float* p, float* m, float* v, float* shadow, con
     if (grid > cap)
         grid = cap;
     if (shadow)
-        adam_bcast_kernel<true><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, shadow, g, tb, (long)n, h, bc1);
+        launch_k(adam_bcast_kernel<true>, (int)grid, OPT_THREADS, 0, s, p, m, v, shadow, g, tb, (long)n, h, bc1);
     else
-        adam_bcast_kernel<false><<<(int)grid, OPT_THREADS, 0, s>>>(p, m, v, shadow, g, tb, (long)n, h, bc1);
+        launch_k(adam_bcast_kernel<false>, (int)grid, OPT_THREADS, 0, s, p, m, v, shadow, g, tb, (long)n, h, bc1);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -343,7 +347,7 @@ void launch_copy_multi(const B200CopyItem* items, int count, cudaStream_t s)
         }
         if (tb.count == 0)
             break;
-        copy_multi_kernel<<<tb.block0[tb.count], OPT_THREADS, 0, s>>>(tb);
+        launch_k(copy_multi_kernel, tb.block0[tb.count], OPT_THREADS, 0, s, tb);
         count_launch();
         B200_CHECK_LAUNCH();
     }
@@ -375,7 +379,7 @@ void launch_adam_ema_step_multi(const B200ParamUpdate* items, int count, float l
         }
         if (tb.count == 0)
             break;
-        adam_multi_kernel<<<tb.block0[tb.count], OPT_THREADS, 0, s>>>(tb, h, bc1);
+        launch_k(adam_multi_kernel, tb.block0[tb.count], OPT_THREADS, 0, s, tb, h, bc1);
         count_launch();
         B200_CHECK_LAUNCH();
     }

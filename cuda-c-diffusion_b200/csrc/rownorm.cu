@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(RN_THREADS) layernorm_fwd_rows(float* __restri
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, long rows, float eps)
 {
+    pdl_prologue();
     constexpr int C = VPT * 128;
     const int lane = threadIdx.x & 31;
     const long warp0 = ((long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5)) * R;
@@ -111,6 +112,7 @@ __global__ void __launch_bounds__(RN_THREADS) layernorm_bwd_rows(float* __restri
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ mu, const float* __restrict__ rstd, long rows)
 {
+    pdl_prologue();
     constexpr int C = VPT * 128;
     __shared__ float fold[2 * C];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -207,6 +209,7 @@ __global__ void __launch_bounds__(RN_THREADS) layernorm_bwd_rows(float* __restri
 __global__ void __launch_bounds__(1024) fold_partials_kernel(float* __restrict__ out_a, float* __restrict__ out_b,
     const float* __restrict__ partials, int nparts, int width, int split)
 {
+    pdl_prologue();
     __shared__ float tile[32][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     float acc = 0.0f;
@@ -231,6 +234,7 @@ template <int VPT, int R>
 __global__ void __launch_bounds__(RN_THREADS) pixelnorm_fwd_rows(float* __restrict__ y, const float* __restrict__ x,
     long rows, float eps)
 {
+    pdl_prologue();
     constexpr int C = VPT * 128;
     const int lane = threadIdx.x & 31;
     const long warp0 = ((long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5)) * R;
@@ -269,6 +273,7 @@ template <int VPT, int R>
 __global__ void __launch_bounds__(RN_THREADS) pixelnorm_bwd_rows(float* __restrict__ dx, const float* __restrict__ dy,
     const float* __restrict__ x, long rows, float eps)
 {
+    pdl_prologue();
     constexpr int C = VPT * 128;
     const int lane = threadIdx.x & 31;
     const long warp0 = ((long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5)) * R;
@@ -324,6 +329,7 @@ __global__ void __launch_bounds__(RN_THREADS) layernorm_fwd_generic(float* __res
     float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, long rows, int C, float eps)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     const long wstride = (long)gridDim.x * RN_WARPS;
     for (long row = (long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5); row < rows; row += wstride) {
@@ -351,6 +357,7 @@ __global__ void __launch_bounds__(RN_THREADS) layernorm_bwd_dx_generic(float* __
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ mu, const float* __restrict__ rstd, long rows, int C)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     const long wstride = (long)gridDim.x * RN_WARPS;
     const float invC = 1.0f / (float)C;
@@ -378,6 +385,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_param_generic(float* __rest
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ mu,
     const float* __restrict__ rstd, long rows, int C, int chunk_rows)
 {
+    pdl_prologue();
     __shared__ float sg[8][33], sb[8][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     const long r0 = (long)blockIdx.y * chunk_rows;
@@ -407,6 +415,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_param_generic(float* __rest
 __global__ void __launch_bounds__(RN_THREADS) pixelnorm_generic(float* __restrict__ out, const float* __restrict__ dy,
     const float* __restrict__ x, long rows, int C, float eps, int backward)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     const long wstride = (long)gridDim.x * RN_WARPS;
     for (long row = (long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5); row < rows; row += wstride) {
@@ -448,7 +457,7 @@ static inline bool fast_rows_ok(int C) { return C % 128 == 0 && C >= 128 && C <=
 void fold_partials(float* out_a, float* out_b, const float* partials, int nparts, int width, int split,
     cudaStream_t s)
 {
-    fold_partials_kernel<<<(width + 31) / 32, dim3(32, 32), 0, s>>>(out_a, out_b, partials, nparts, width, split);
+    launch_k(fold_partials_kernel, (width + 31) / 32, dim3(32, 32), 0, s, out_a, out_b, partials, nparts, width, split);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -479,10 +488,10 @@ void launch_layernorm_forward(float* y, float* mu, float* rstd, const float* x, 
         return;
     const long rows = batch;
     if (fast_rows_ok(C) && aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)) {
-        RN_DISPATCH_VPT(C, (layernorm_fwd_rows<VPT, R><<<rows_grid(rows, RN_WARPS * R, "ln_blocks_per_sm", 8),
-                                RN_THREADS, 0, s>>>(y, mu, rstd, x, gamma, beta, rows, eps)));
+        RN_DISPATCH_VPT(C, (launch_k(layernorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "ln_blocks_per_sm", 8),
+                                RN_THREADS, 0, s, y, mu, rstd, x, gamma, beta, rows, eps)));
     } else {
-        layernorm_fwd_generic<<<rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s>>>(
+        launch_k(layernorm_fwd_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s,
             y, mu, rstd, x, gamma, beta, rows, C, eps);
     }
     count_launch();
@@ -500,7 +509,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
         const int R = (C / 128 == 1) ? 4 : (C / 128 == 2 ? 2 : 1);
         const int grid = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 4);
         B200_REQUIRE(scratch_get(s, (size_t)grid * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
-        RN_DISPATCH_VPT(C, (layernorm_bwd_rows<VPT, R><<<grid, RN_THREADS, 0, s>>>(grad_in, sc.partials, grad_out, x,
+        RN_DISPATCH_VPT(C, (launch_k(layernorm_bwd_rows<VPT, R>, grid, RN_THREADS, 0, s, grad_in, sc.partials, grad_out, x,
                                 gamma, mu, rstd, rows)));
         count_launch();
         B200_CHECK_LAUNCH();
@@ -508,7 +517,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
         return;
     }
     if (rows > 0) {
-        layernorm_bwd_dx_generic<<<rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s>>>(
+        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s,
             grad_in, grad_out, x, gamma, mu, rstd, rows, C);
         count_launch();
         B200_CHECK_LAUNCH();
@@ -517,7 +526,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
     const int nchunks = rows > 0 ? (int)((rows + chunk_rows - 1) / chunk_rows) : 1;
     B200_REQUIRE(nchunks <= 65535, "layernorm_backward: too many rows for the generic path");
     B200_REQUIRE(scratch_get(s, (size_t)nchunks * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
-    layernorm_bwd_param_generic<<<dim3((C + 31) / 32, nchunks), dim3(32, 8), 0, s>>>(sc.partials, grad_out, x, mu,
+    launch_k(layernorm_bwd_param_generic, dim3((C + 31) / 32, nchunks), dim3(32, 8), 0, s, sc.partials, grad_out, x, mu,
         rstd, rows, C, chunk_rows);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -531,10 +540,10 @@ void launch_pixel_norm_forward(float* y, const float* x, int rows_i, int C, floa
         return;
     const long rows = rows_i;
     if (fast_rows_ok(C) && aligned16(y) && aligned16(x)) {
-        RN_DISPATCH_VPT(C, (pixelnorm_fwd_rows<VPT, R><<<rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
-                                RN_THREADS, 0, s>>>(y, x, rows, eps)));
+        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
+                                RN_THREADS, 0, s, y, x, rows, eps)));
     } else {
-        pixelnorm_generic<<<rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s>>>(y, nullptr, x,
+        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s, y, nullptr, x,
             rows, C, eps, 0);
     }
     count_launch();
@@ -549,10 +558,10 @@ void launch_pixel_norm_backward(float* dx, const float* dy, const float* x, int 
         return;
     const long rows = rows_i;
     if (fast_rows_ok(C) && aligned16(dx) && aligned16(dy) && aligned16(x)) {
-        RN_DISPATCH_VPT(C, (pixelnorm_bwd_rows<VPT, R><<<rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
-                                RN_THREADS, 0, s>>>(dx, dy, x, rows, eps)));
+        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_bwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
+                                RN_THREADS, 0, s, dx, dy, x, rows, eps)));
     } else {
-        pixelnorm_generic<<<rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s>>>(dx, dy, x, rows,
+        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s, dx, dy, x, rows,
             C, eps, 1);
     }
     count_launch();
@@ -644,7 +653,7 @@ extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, 
         return -3;
     if (fast) {
         const int grid = (int)nparts;
-        RN_DISPATCH_VPT(C, (layernorm_bwd_rows<VPT, R><<<grid, RN_THREADS, 0, s>>>(grad_in, scratch, grad_out, x, gamma,
+        RN_DISPATCH_VPT(C, (launch_k(layernorm_bwd_rows<VPT, R>, grid, RN_THREADS, 0, s, grad_in, scratch, grad_out, x, gamma,
                                 mu, rstd, rows)));
         count_launch();
         B200_CHECK_LAUNCH();
@@ -652,12 +661,12 @@ extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, 
         return 0;
     }
     if (rows > 0) {
-        layernorm_bwd_dx_generic<<<rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s>>>(grad_in,
+        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s, grad_in,
             grad_out, x, gamma, mu, rstd, rows, C);
         count_launch();
         B200_CHECK_LAUNCH();
     }
-    layernorm_bwd_param_generic<<<dim3((C + 31) / 32, (unsigned)nparts), dim3(32, 8), 0, s>>>(scratch, grad_out, x, mu,
+    launch_k(layernorm_bwd_param_generic, dim3((C + 31) / 32, (unsigned)nparts), dim3(32, 8), 0, s, scratch, grad_out, x, mu,
         rstd, rows, C, chunk_rows);
     count_launch();
     B200_CHECK_LAUNCH();

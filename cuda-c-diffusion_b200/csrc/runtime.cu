@@ -7,6 +7,7 @@
 #include <map>
 #include <mutex>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string>
 #include <string.h>
 #include <utility>
@@ -77,9 +78,35 @@ int sm_count()
     return cached[dev];
 }
 
+// Tunables can also come from the environment, for programs that only link the library:
+// B200_TUNE="key=int,key=int" is read once, before the first lookup; b200_tune_set overrides it.
+static void tune_from_environment_locked()
+{
+    static bool done = false;
+    if (done)
+        return;
+    done = true;
+    const char* env = getenv("B200_TUNE");
+    if (!env)
+        return;
+    std::string all(env);
+    size_t at = 0;
+    while (at < all.size()) {
+        size_t end = all.find(',', at);
+        if (end == std::string::npos)
+            end = all.size();
+        const std::string item = all.substr(at, end - at);
+        const size_t eq = item.find('=');
+        if (eq != std::string::npos && eq > 0 && !g_tunables.count(item.substr(0, eq)))
+            g_tunables[item.substr(0, eq)] = atoi(item.c_str() + eq + 1);
+        at = end + 1;
+    }
+}
+
 int tune_lookup(const char* key, int dflt)
 {
     std::lock_guard<std::mutex> lk(g_mu);
+    tune_from_environment_locked();
     auto it = g_tunables.find(key);
     return it == g_tunables.end() ? dflt : it->second;
 }

@@ -33,6 +33,7 @@ template <int V>
 __global__ void __launch_bounds__(256) im2col_kernel(float* __restrict__ col, const float* __restrict__ im, int H, int W,
     int C, int K, int stride, int pad, int Ho, int Wo, long total)
 {
+    pdl_prologue();
     const int Cv = C / V;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         long tmp = i;
@@ -60,6 +61,7 @@ template <int KT>
 __global__ void __launch_bounds__(256) im2col_taps_kernel(float4* __restrict__ col, const float4* __restrict__ im,
     int H, int W, int Cv, int K, int stride, int pad, int Ho, int Wo, unsigned total)
 {
+    pdl_prologue();
     const int Kk = KT ? KT : K;
     const unsigned row4 = (unsigned)(Kk * Kk) * (unsigned)Cv;  // float4 per col row
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -88,6 +90,7 @@ template <int V>
 __global__ void __launch_bounds__(256) col2im_gather_kernel(float* __restrict__ grad_im,
     const float* __restrict__ grad_col, int H, int W, int C, int K, int stride, int pad, int Ho, int Wo, long total)
 {
+    pdl_prologue();
     const int Cv = C / V;
     const long KKC = (long)K * K * C;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -136,6 +139,7 @@ template <int KT, bool ASSIGN>
 __global__ void __launch_bounds__(256) col2im_taps_kernel(float4* __restrict__ grad_im,
     const float4* __restrict__ grad_col, int H, int W, int Cv, int K, int pad, int Ho, int Wo, unsigned total)
 {
+    pdl_prologue();
     const int Kk = KT ? KT : K;
     const unsigned row4 = (unsigned)(Kk * Kk) * (unsigned)Cv;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -176,6 +180,7 @@ template <int MODE, int V>
 __global__ void __launch_bounds__(256) resample_kernel(float* __restrict__ dst, const float* __restrict__ src, int H,
     int W, int C, long total)
 {
+    pdl_prologue();
     const int Cv = C / V;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         long tmp = i;
@@ -234,6 +239,7 @@ template <int V>
 __global__ void __launch_bounds__(256) permute_0213_kernel(float* __restrict__ out, const float* __restrict__ in, int d1,
     int d2, int d3, long total)
 {
+    pdl_prologue();
     const int d3v = d3 / V;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         long tmp = i;
@@ -251,6 +257,7 @@ __global__ void __launch_bounds__(256) permute_0213_kernel(float* __restrict__ o
 __global__ void __launch_bounds__(256) attn_softmax_kernel(float* out, const float* in, int N,
     int S)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     for (long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); row < N; row += (long)gridDim.x * 8) {
         const float* x = in + row * S;
@@ -276,6 +283,7 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(float* out, const flo
 __global__ void __launch_bounds__(256) attn_softmax_backward_kernel(float* __restrict__ gi, const float* __restrict__ go,
     const float* __restrict__ p, int N, int S)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     for (long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); row < N; row += (long)gridDim.x * 8) {
         const float* g = go + row * S;
@@ -293,6 +301,7 @@ __global__ void __launch_bounds__(256) attn_softmax_backward_kernel(float* __res
 __global__ void __launch_bounds__(256) softmax_xent_kernel(float* __restrict__ grad, float* __restrict__ loss_row,
     const float* __restrict__ logits, const int* __restrict__ targets, int batch, int C)
 {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     for (long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); row < batch; row += (long)gridDim.x * 8) {
         const float* z = logits + row * C;
@@ -327,6 +336,7 @@ __global__ void __launch_bounds__(256) strip_reduce_kernel(float* __restrict__ o
     const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ cond, int rows_per_group, int C,
     long total_rows)
 {
+    pdl_prologue();
     __shared__ float part[8][33];
     const int col = blockIdx.x * 32 + threadIdx.x;
     const long r0 = (long)blockIdx.y * rows_per_group;
@@ -361,6 +371,7 @@ __global__ void __launch_bounds__(256) strip_reduce_kernel(float* __restrict__ o
 __global__ void __launch_bounds__(256) mse_kernel(float* __restrict__ grad, float* __restrict__ loss_row,
     const float* __restrict__ pred, const float* __restrict__ target, int batch, int dim)
 {
+    pdl_prologue();
     __shared__ float buf[32];
     const size_t base = (size_t)blockIdx.x * dim;
     const float inv = 2.0f / (float)(batch * dim);
@@ -382,9 +393,9 @@ static void resample_launch(float* dst, const float* src, int batch, int H, int 
     const bool vec = C % 4 == 0 && aligned16(dst) && aligned16(src);
     if (vec) {
         const long total = small_or_big_elems / 4;
-        resample_kernel<MODE, 4><<<flat_grid(total), 256, 0, s>>>(dst, src, H, W, C, total);
+        launch_k(resample_kernel<MODE, 4>, flat_grid(total), 256, 0, s, dst, src, H, W, C, total);
     } else {
-        resample_kernel<MODE, 1><<<flat_grid(small_or_big_elems), 256, 0, s>>>(dst, src, H, W, C, small_or_big_elems);
+        launch_k(resample_kernel<MODE, 1>, flat_grid(small_or_big_elems), 256, 0, s, dst, src, H, W, C, small_or_big_elems);
     }
     count_launch();
     B200_CHECK_LAUNCH();
@@ -409,15 +420,15 @@ void launch_im2col(float* col, const float* im, int batch, int H, int W, int C, 
         const float4* im4 = reinterpret_cast<const float4*>(im);
         float4* col4 = reinterpret_cast<float4*>(col);
         if (K == 3)
-            im2col_taps_kernel<3><<<flat_grid(units), 256, 0, s>>>(col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
+            launch_k(im2col_taps_kernel<3>, flat_grid(units), 256, 0, s, col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
                 (unsigned)units);
         else
-            im2col_taps_kernel<0><<<flat_grid(units), 256, 0, s>>>(col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
+            launch_k(im2col_taps_kernel<0>, flat_grid(units), 256, 0, s, col4, im4, H, W, C / 4, K, stride, pad, H_out, W_out,
                 (unsigned)units);
     } else if (C % 4 == 0 && aligned16(col) && aligned16(im))
-        im2col_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(col, im, H, W, C, K, stride, pad, H_out, W_out, n / 4);
+        launch_k(im2col_kernel<4>, flat_grid(n / 4), 256, 0, s, col, im, H, W, C, K, stride, pad, H_out, W_out, n / 4);
     else
-        im2col_kernel<1><<<flat_grid(n), 256, 0, s>>>(col, im, H, W, C, K, stride, pad, H_out, W_out, n);
+        launch_k(im2col_kernel<1>, flat_grid(n), 256, 0, s, col, im, H, W, C, K, stride, pad, H_out, W_out, n);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -434,13 +445,13 @@ static bool col2im_fast(float* grad_im, const float* grad_col, int batch, int H,
     const int grid = flat_grid(n / 4);
     const unsigned total = (unsigned)(n / 4);
     if (K == 3 && assign)
-        col2im_taps_kernel<3, true><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+        launch_k(col2im_taps_kernel<3, true>, grid, 256, 0, s, gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
     else if (K == 3)
-        col2im_taps_kernel<3, false><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+        launch_k(col2im_taps_kernel<3, false>, grid, 256, 0, s, gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
     else if (assign)
-        col2im_taps_kernel<0, true><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+        launch_k(col2im_taps_kernel<0, true>, grid, 256, 0, s, gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
     else
-        col2im_taps_kernel<0, false><<<grid, 256, 0, s>>>(gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
+        launch_k(col2im_taps_kernel<0, false>, grid, 256, 0, s, gi4, gc4, H, W, C / 4, K, pad, H_out, W_out, total);
     count_launch();
     B200_CHECK_LAUNCH();
     return true;
@@ -457,10 +468,10 @@ void launch_col2im(float* grad_im, const float* grad_col, int batch, int H, int 
     if (col2im_fast(grad_im, grad_col, batch, H, W, C, K, stride, pad, H_out, W_out, false, s))
         return;
     if (C % 4 == 0 && aligned16(grad_im) && aligned16(grad_col))
-        col2im_gather_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(grad_im, grad_col, H, W, C, K, stride, pad, H_out,
+        launch_k(col2im_gather_kernel<4>, flat_grid(n / 4), 256, 0, s, grad_im, grad_col, H, W, C, K, stride, pad, H_out,
             W_out, n / 4);
     else
-        col2im_gather_kernel<1><<<flat_grid(n), 256, 0, s>>>(grad_im, grad_col, H, W, C, K, stride, pad, H_out, W_out,
+        launch_k(col2im_gather_kernel<1>, flat_grid(n), 256, 0, s, grad_im, grad_col, H, W, C, K, stride, pad, H_out, W_out,
             n);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -520,7 +531,7 @@ void launch_attn_softmax(float* out, const float* in, int N, int S, cudaStream_t
     B200_REQUIRE(N >= 0 && S > 0, "attn_softmax: N=%d S=%d", N, S);
     if (N == 0)
         return;
-    attn_softmax_kernel<<<flat_grid((long)N, 8), 256, 0, s>>>(out, in, N, S);
+    launch_k(attn_softmax_kernel, flat_grid((long)N, 8), 256, 0, s, out, in, N, S);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -531,7 +542,7 @@ void launch_attn_softmax_backward(float* grad_in, const float* grad_out, const f
     B200_REQUIRE(N >= 0 && S > 0, "attn_softmax_backward: N=%d S=%d", N, S);
     if (N == 0)
         return;
-    attn_softmax_backward_kernel<<<flat_grid((long)N, 8), 256, 0, s>>>(grad_in, grad_out, p, N, S);
+    launch_k(attn_softmax_backward_kernel, flat_grid((long)N, 8), 256, 0, s, grad_in, grad_out, p, N, S);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -543,9 +554,9 @@ void launch_permute_0213(float* out, const float* in, int B, int d1, int d2, int
     if (n == 0)
         return;
     if (d3 % 4 == 0 && aligned16(out) && aligned16(in))
-        permute_0213_kernel<4><<<flat_grid(n / 4), 256, 0, s>>>(out, in, d1, d2, d3, n / 4);
+        launch_k(permute_0213_kernel<4>, flat_grid(n / 4), 256, 0, s, out, in, d1, d2, d3, n / 4);
     else
-        permute_0213_kernel<1><<<flat_grid(n), 256, 0, s>>>(out, in, d1, d2, d3, n);
+        launch_k(permute_0213_kernel<1>, flat_grid(n), 256, 0, s, out, in, d1, d2, d3, n);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -556,7 +567,7 @@ void launch_spatial_modulate_backward(float* grad_in, float* grad_cond, const fl
     B200_REQUIRE(batch >= 0 && batch <= 65535 && H > 0 && W > 0 && C > 0, "spatial_modulate_backward: bad extents");
     if (batch == 0)
         return;
-    strip_reduce_kernel<1><<<dim3((C + 31) / 32, batch), dim3(32, 8), 0, s>>>(grad_cond, grad_in, grad_out, in, cond,
+    launch_k(strip_reduce_kernel<1>, dim3((C + 31) / 32, batch), dim3(32, 8), 0, s, grad_cond, grad_in, grad_out, in, cond,
         H * W, C, (long)batch * H * W);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -567,7 +578,7 @@ void launch_spatial_reduce_sum(float* out, const float* in, int batch, int HW, i
     B200_REQUIRE(batch >= 0 && batch <= 65535 && HW > 0 && C > 0, "spatial_reduce_sum: bad extents");
     if (batch == 0)
         return;
-    strip_reduce_kernel<0><<<dim3((C + 31) / 32, batch), dim3(32, 8), 0, s>>>(out, nullptr, in, nullptr, nullptr, HW,
+    launch_k(strip_reduce_kernel<0>, dim3((C + 31) / 32, batch), dim3(32, 8), 0, s, out, nullptr, in, nullptr, nullptr, HW,
         C, (long)batch * HW);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -585,7 +596,7 @@ void launch_bias_grad(float* gb, const float* grad_out, int batch, int N, cudaSt
     if (want > most)
         want = most;
     if (want <= 1) {
-        strip_reduce_kernel<0><<<dim3(col_ctas, 1), dim3(32, 8), 0, s>>>(gb, nullptr, grad_out, nullptr, nullptr, batch,
+        launch_k(strip_reduce_kernel<0>, dim3(col_ctas, 1), dim3(32, 8), 0, s, gb, nullptr, grad_out, nullptr, nullptr, batch,
             N, (long)batch);
         count_launch();
         B200_CHECK_LAUNCH();
@@ -595,7 +606,7 @@ void launch_bias_grad(float* gb, const float* grad_out, int batch, int N, cudaSt
     const int per = (batch + groups - 1) / groups;
     Scratch sc;
     B200_REQUIRE(scratch_get(s, (size_t)groups * N, 0, &sc), "bias_grad: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
-    strip_reduce_kernel<0><<<dim3(col_ctas, groups), dim3(32, 8), 0, s>>>(sc.partials, nullptr, grad_out, nullptr,
+    launch_k(strip_reduce_kernel<0>, dim3(col_ctas, groups), dim3(32, 8), 0, s, sc.partials, nullptr, grad_out, nullptr,
         nullptr, per, N, (long)batch);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -608,7 +619,7 @@ void launch_mse_fwd_bwd(float* grad, float* loss_row, const float* pred, const f
     B200_REQUIRE(batch >= 0 && dim > 0, "mse_fwd_bwd: batch=%d dim=%d", batch, dim);
     if (batch == 0)
         return;
-    mse_kernel<<<batch, 256, 0, s>>>(grad, loss_row, pred, target, batch, dim);
+    launch_k(mse_kernel, batch, 256, 0, s, grad, loss_row, pred, target, batch, dim);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -619,7 +630,7 @@ void launch_softmax_xent(float* grad_logits, float* loss_row, const float* logit
     B200_REQUIRE(batch >= 0 && C > 0, "softmax_xent: batch=%d C=%d", batch, C);
     if (batch == 0)
         return;
-    softmax_xent_kernel<<<flat_grid((long)batch, 8), 256, 0, s>>>(grad_logits, loss_row, logits, targets, batch, C);
+    launch_k(softmax_xent_kernel, flat_grid((long)batch, 8), 256, 0, s, grad_logits, loss_row, logits, targets, batch, C);
     count_launch();
     B200_CHECK_LAUNCH();
 }

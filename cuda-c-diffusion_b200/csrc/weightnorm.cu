@@ -73,6 +73,7 @@ __device__ __forceinline__ float wn_fold_lanes(float (*fold)[WN_COLS + 1], int q
 // grid = (CS, total strips), cluster = (CS,1,1), block = 256 = 8 float4 columns x 32 row lanes
 __global__ void __launch_bounds__(WN_THREADS) wn_forward_cluster(const WnTable tb, const float eps)
 {
+    pdl_prologue();
     __shared__ float fold[32][WN_COLS + 1];
     __shared__ float colsum[WN_COLS];  // read by cluster peers
     __shared__ float colinv[WN_COLS];
@@ -155,6 +156,7 @@ __device__ __forceinline__ int wn_find_grad(const WnGradTable& tb, int strip)
 // grid = (CS, total strips), cluster = (CS,1,1)
 __global__ void __launch_bounds__(WN_THREADS) wn_backward_cluster(const WnGradTable tb)
 {
+    pdl_prologue();
     __shared__ float fold[32][WN_COLS + 1];
     __shared__ float colsum[WN_COLS];
     __shared__ float coldot[WN_COLS];
@@ -226,6 +228,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256) wn_strip(float* __restrict__ A, const float* __restrict__ Wn,
     const float* __restrict__ gain, float* __restrict__ g_gain, int in, int out, float eps)
 {
+    pdl_prologue();
     __shared__ float part[8][33];
     __shared__ float colv[32];
     const int col = blockIdx.x * 32 + threadIdx.x;
@@ -280,7 +283,7 @@ static bool wn_cluster_ok(const void* p, int in, int out)
 static void wn_launch_cluster_fwd(const WnTable& tb, int cs, float eps, cudaStream_t s)
 {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.gridDim = dim3((unsigned)cs, (unsigned)tb.strip0[tb.count], 1);
     cfg.blockDim = dim3(WN_THREADS, 1, 1);
     cfg.stream = s;
@@ -288,8 +291,10 @@ static void wn_launch_cluster_fwd(const WnTable& tb, int cs, float eps, cudaStre
     attr[0].val.clusterDim.x = (unsigned)cs;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    unsigned nat = 1;
+    pdl_attribute(attr, &nat);
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, wn_forward_cluster, tb, eps);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -302,7 +307,7 @@ static void wn_launch_cluster_fwd(const WnTable& tb, int cs, float eps, cudaStre
 static void wn_launch_cluster_bwd(const WnGradTable& tb, int cs, cudaStream_t s)
 {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.gridDim = dim3((unsigned)cs, (unsigned)tb.strip0[tb.count], 1);
     cfg.blockDim = dim3(WN_THREADS, 1, 1);
     cfg.stream = s;
@@ -310,8 +315,10 @@ static void wn_launch_cluster_bwd(const WnGradTable& tb, int cs, cudaStream_t s)
     attr[0].val.clusterDim.x = (unsigned)cs;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    unsigned nat = 1;
+    pdl_attribute(attr, &nat);
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, wn_backward_cluster, tb);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -371,7 +378,7 @@ static void weight_normalize_now(float* W, int in, int out, float eps, cudaStrea
         wn_launch_cluster_fwd(tb, wn_cluster_size(in), eps, s);
         return;
     }
-    wn_strip<0><<<(out + 31) / 32, dim3(32, 8), 0, s>>>(W, nullptr, nullptr, nullptr, in, out, eps);
+    launch_k(wn_strip<0>, (out + 31) / 32, dim3(32, 8), 0, s, W, nullptr, nullptr, nullptr, in, out, eps);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -420,7 +427,7 @@ static void weight_normalize_backward_now(float* gW, const float* Wn, const floa
         wn_launch_cluster_bwd(tb, wn_cluster_size(in), s);
         return;
     }
-    wn_strip<1><<<(out + 31) / 32, dim3(32, 8), 0, s>>>(gW, Wn, gain, g_gain, in, out, 0.0f);
+    launch_k(wn_strip<1>, (out + 31) / 32, dim3(32, 8), 0, s, gW, Wn, gain, g_gain, in, out, 0.0f);
     count_launch();
     B200_CHECK_LAUNCH();
 }
