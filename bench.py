@@ -376,8 +376,9 @@ def graph_time(lib, fn, nsets, reps, scratch_bytes=0):
     return e0.elapsed_time(e1) * 1e-3 / reps
 
 
-def ops_table(lib, fused, peak):
-    """Every other kernel of the path at the baseline's sizes: seconds per launch and algorithmic GB/s."""
+def ops_table(lib, fused, peak, only=None):
+    """Every other kernel of the path at the baseline's sizes: seconds per launch and algorithmic GB/s.
+    `only` = "cfg0" restricts the table to the first configuration (profiler captures of that shape)."""
     dev = torch.device("cuda")
     st = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     out = {}
@@ -405,6 +406,8 @@ def ops_table(lib, fused, peak):
     add("cfg0_groupnorm_fwd", graph_time(lib, fw, ns, 100), 2 * n * 4)
     add("cfg0_groupnorm_bwd", graph_time(lib, bw, ns, 100, 2 * b * c * 4), 3 * n * 4)
     del xs, ys, dys
+    if only == "cfg0":
+        return out
 
     # ---- config 1: EDM magnitude-preserving ops on [256,28,28,128]
     n = 256 * 28 * 28 * 128
@@ -643,6 +646,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--blocks", type=int, default=5, help="timed blocks of --steps steps; the median block is reported")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table")
+    ap.add_argument("--ops-only", metavar="CFG", help="print only the per-op table of one configuration (cfg0) and exit")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--no-trainer", action="store_true", help="skip the EDM trainer legs (profiler captures)")
@@ -685,6 +689,9 @@ def main():
             key, val = kv.split("=")
             lib.b200_tune_set(key.encode(), int(val))
     peak, peak_src = measured_peak()
+    if args.ops_only:
+        print(json.dumps({"ops": ops_table(lib, True, peak, only=args.ops_only)}))
+        return
     fused = True
     ref_note = None
     if args.impl == "reference":

@@ -12,9 +12,13 @@
 //   3. generic kernels (this file): any shape, any alignment (C % 4 != 0, misaligned pointers) and the
 //      activations the strips do not instantiate.
 //
-// (A fourth family -- persistent thread-block clusters on 2-D TMA tiles with a DSMEM combine -- was
-// built and measured at 0.44-0.48 of the copy peak against 0.8 for the strips on every shape, with the
-// cluster barrier and the DSMEM round trip on each item's critical path; it has been removed.)
+// Two more families were built, measured and removed.  Persistent thread-block clusters on 2-D TMA
+// tiles with a DSMEM combine: 0.44-0.48 of the copy peak against 0.8 for the strips on every shape (the
+// cluster barrier and the DSMEM round trip sit on each item's critical path).  Two passes of fully
+// contiguous streaming kernels per 16-80 MB chunk of samples, the second pass reading from L2: correct,
+// but [256,32,32,256] took 174-290 us forward and 340-690 us backward against 100 / 155 us for the
+// strips: a chunk small enough to stay in L2 is too small a launch to reach the HBM rate, and only about
+// half of the second pass's reads hit L2.
 //
 // Backward in every family reuses the per-channel sums of g and g*xhat (g = dy * act'(z)) for BOTH
 // the group sums that dx needs and the per-sample dgamma/dbeta partials, which a fixed-order fold

@@ -651,25 +651,33 @@ extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, 
     float* scratch = ln_noalloc_scratch_address();
     if (!scratch)
         return -3;
+    // a launch that fails is reported (b200_set_error_mode) AND ends the call with -4: nothing later in
+    // the sequence runs on results that were never produced
+#define NOALLOC_LAUNCHED()                                        \
+    do {                                                          \
+        count_launch();                                           \
+        const cudaError_t le_ = cudaPeekAtLastError();            \
+        B200_CHECK_LAUNCH();                                      \
+        if (le_ != cudaSuccess)                                   \
+            return -4;                                            \
+    } while (0)
     if (fast) {
         const int grid = (int)nparts;
         RN_DISPATCH_VPT(C, (launch_k(layernorm_bwd_rows<VPT, R>, grid, RN_THREADS, 0, s, grad_in, scratch, grad_out, x, gamma,
                                 mu, rstd, rows)));
-        count_launch();
-        B200_CHECK_LAUNCH();
+        NOALLOC_LAUNCHED();
         fold_partials(ggamma, gbeta, scratch, grid, 2 * C, C, s);
-        return 0;
+        return cudaPeekAtLastError() == cudaSuccess ? 0 : -4;
     }
     if (rows > 0) {
         launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s, grad_in,
             grad_out, x, gamma, mu, rstd, rows, C);
-        count_launch();
-        B200_CHECK_LAUNCH();
+        NOALLOC_LAUNCHED();
     }
     launch_k(layernorm_bwd_param_generic, dim3((C + 31) / 32, (unsigned)nparts), dim3(32, 8), 0, s, scratch, grad_out, x, mu,
         rstd, rows, C, chunk_rows);
-    count_launch();
-    B200_CHECK_LAUNCH();
+    NOALLOC_LAUNCHED();
+#undef NOALLOC_LAUNCHED
     fold_partials(ggamma, gbeta, scratch, (int)nparts, 2 * C, C, s);
-    return 0;
+    return cudaPeekAtLastError() == cudaSuccess ? 0 : -4;
 }

@@ -351,12 +351,15 @@ void launch_weight_normalize(float* W, int in, int out, float eps, cudaStream_t 
     B200_REQUIRE(in > 0 && out > 0, "weight_normalize: in=%d out=%d", in, out);
     {
         std::lock_guard<std::mutex> lk(g_wn.mu);
-        if (g_wn.mode == 2)
-            return;  // the driver normalises every recorded weight itself (b200_wn_forward_all)
-        if (g_wn.mode == 1) {
+        if (g_wn.mode != 0) {
             bool seen = false;
             for (const B200WeightDesc& d : g_wn.fwd)
                 seen = seen || d.W == W;
+            // mode 2: the driver has normalised every RECORDED weight itself (b200_wn_forward_all).  A weight
+            // that was never recorded (a layer first used after the recording pass, a second model in the
+            // process) is normalised here and now, and joins the set for the following passes.
+            if (seen && g_wn.mode == 2)
+                return;
             if (!seen)
                 g_wn.fwd.push_back(B200WeightDesc{ W, in, out });
             g_wn.eps = eps;

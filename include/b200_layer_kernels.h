@@ -222,8 +222,9 @@ void launch_weight_normalize_backward_multi(const B200WeightGradDesc* items, int
    driver owns the training step.  Modes:
      0  off (default).
      1  record: calls execute as usual; the forward calls' (W, in, out, eps) are remembered (one entry per W).
-     2  batched: launch_weight_normalize returns at once - the driver has normalised every recorded weight
-        with b200_wn_forward_all since the last parameter update; launch_weight_normalize_backward only
+     2  batched: launch_weight_normalize returns at once for every RECORDED weight - the driver has normalised
+        those with b200_wn_forward_all since the last parameter update; a weight that was never recorded (a
+        layer first used after the recording pass, another model) is normalised at once and joins the set; launch_weight_normalize_backward only
         queues its arguments, and b200_wn_backward_flush runs the queue as one launch.  Nothing between a
         module's backward and the optimizer reads gW or g_gain, so the deferral does not change results.
    The state is per process, not per stream: one training loop at a time.  b200_wn_forward_all and
@@ -291,7 +292,9 @@ void launch_copy_multi(const B200CopyItem* items, int count, cudaStream_t s);
    4 MiB array that is part of the library image (every GPU that loads the library carries it
    until the process exits) instead of the on-demand scratch arena.
    - Returns 0 on success; a negative value (and an error report, see b200_set_error_mode)
-     when batch/C need more partial rows than the array holds: for C a multiple of 128 up to
+     otherwise: -1 bad extents, -2 the shape needs more partial rows than the array holds, -3 the
+     array's address could not be looked up, -4 a kernel launch failed (nothing after it ran).
+     The size rule: for C a multiple of 128 up to
      1024 every batch fits; otherwise ceil(batch/256) * 2*C floats must be <= 1048576.
    - The first call on each device looks up the array's device address (that device must be
      current); make that first call before starting any stream capture.

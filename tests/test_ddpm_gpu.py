@@ -134,3 +134,14 @@ def test_ddpm_trainer_matches_reference_kernels_to_the_reference_own_spread(tmp_
         assert max(dists) <= 2.0 * spread + 1e-4
     elif finite:
         assert max(dists) <= 5e-2
+
+
+def test_ddpm_block_gradients_by_central_differences():
+    """tests/host/ddpm_block_gradcheck.c: the replaced residual block (fused GroupNorm+SiLU, recomputed
+    pre-activation) against central differences of L = <forward(x), g> for the input, the time embedding
+    and every parameter tensor, three block shapes."""
+    _need(BIN / "ddpm_block_gradcheck")
+    res = subprocess.run([str(BIN / "ddpm_block_gradcheck")], capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "0 failure(s)" in res.stdout and res.stdout.count("PASS") == 3 * 12 and "FAIL" not in res.stdout

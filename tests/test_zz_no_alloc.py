@@ -37,17 +37,45 @@ def _run(lib, fn, rows, C, seed, keep):
     return rc, dx.cpu().numpy(), dg.cpu().numpy(), db.cpu().numpy()
 
 
-@pytest.mark.parametrize("shapes", [[(3000, 256), (777, 256)], [(500, 100), (4100, 384)]])
+def _free_bytes():
+    import torch
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]  # cudaMemGetInfo: free bytes of the device, all allocators included
+
+
+# the last two pairs reach the limits of the fixed array: C = 1024 / 896 with enough rows that the grid (4 CTAs
+# per SM) has to be clipped to the partial rows that fit (2^20 / 2048 = 512 CTAs; the grid-stride loop covers
+# the rest), and the generic path (C not a multiple of 128) with ceil(rows/256) * 2*C just under 2^20 floats
+@pytest.mark.parametrize("shapes", [[(3000, 256), (777, 256)], [(500, 100), (4100, 384)],
+                                    [(6000, 1024), (5000, 896)], [(256 * 2600, 200), (1000, 200)]])
 def test_noalloc_backward_matches_regular_backward_twice_in_a_row(lib, shapes):
     keep = []
     for i, (rows, C) in enumerate(shapes):
+        # the regular entry point first: it (and torch) may allocate; what follows must not
+        _, rdx, rdg, rdb = _run(lib, lib.launch_layernorm_backward, rows, C, 100 + i, keep)
+        _run(lib, lib.launch_layernorm_backward_noalloc, rows, C, 100 + i, keep)  # first use on this device: set-up
+        import torch
+        rng = np.random.default_rng(100 + i)
+        t = [torch.from_numpy(rng.standard_normal((rows, C), dtype=np.float32)).cuda() for _ in range(2)]
+        gamma = torch.from_numpy((1 + 0.1 * rng.standard_normal(C)).astype(np.float32)).cuda()
+        mu, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+        y, dxb = torch.empty_like(t[0]), torch.empty_like(t[0])
+        dgb, dbb = torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        P = lambda a: ctypes.c_void_p(a.data_ptr())
+        lib.launch_layernorm_forward(P(y), P(mu), P(rstd), P(t[0]), P(gamma), P(dgb), rows, C, ctypes.c_float(1e-5), st)
+        before = _free_bytes()
+        rc0 = lib.launch_layernorm_backward_noalloc(P(dxb), P(dgb), P(dbb), P(t[1]), P(t[0]), P(gamma), P(mu), P(rstd),
+                                                    rows, C, st)
+        assert rc0 == 0 and _free_bytes() == before, "the allocation-free entry point changed the device's free memory"
+        del t, y, dxb
         rc, dx, dg, db = _run(lib, lib.launch_layernorm_backward_noalloc, rows, C, 100 + i, keep)
         assert rc == 0
-        _, rdx, rdg, rdb = _run(lib, lib.launch_layernorm_backward, rows, C, 100 + i, keep)
         assert cases.rel_err(dx, rdx) <= cases.TOL_BWD
         assert cases.rel_err(dg, rdg) <= cases.TOL_BWD
         assert cases.rel_err(db, rdb) <= cases.TOL_BWD
         assert np.isfinite(dx).all() and np.isfinite(dg).all() and np.isfinite(db).all()
+        keep.clear()
 
 
 def test_noalloc_backward_rejects_sizes_beyond_its_fixed_scratch(lib):
