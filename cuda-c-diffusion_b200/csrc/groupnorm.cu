@@ -18,7 +18,10 @@
 // contiguous streaming kernels per 16-80 MB chunk of samples, the second pass reading from L2: correct,
 // but [256,32,32,256] took 174-290 us forward and 340-690 us backward against 100 / 155 us for the
 // strips: a chunk small enough to stay in L2 is too small a launch to reach the HBM rate, and only about
-// half of the second pass's reads hit L2.
+// half of the second pass's reads hit L2.  And for small launches, where a strip's latency chain rather
+// than bandwidth sets the time, the rows of a strip split over a cluster of 2 or 4 CTAs with one DSMEM
+// exchange of the partial sums: [128,28,28,64] took 15.7-37 us forward and 28-41 us backward against
+// 12.2 / 18.0 us for the plain strips -- two cluster barriers cost more than half a strip's latency.
 //
 // Backward in every family reuses the per-channel sums of g and g*xhat (g = dy * act'(z)) for BOTH
 // the group sums that dx needs and the per-sample dgamma/dbeta partials, which a fixed-order fold
