@@ -634,7 +634,7 @@ KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd"
 # (captured at batch 128 and scaled by 2 to the full launch; traffic grows linearly with the batch).  Reads
 # match the algorithmic bytes; the write figure is low because up to an L2's worth of dirty lines has
 # not been written back when the kernel ends.
-NCU_TRAFFIC = {"gn_silu_bwd": 2 * (268_560_128 + 95_581_696), "gn_silu_fwd": 2 * (134_922_240 + 82_007_552),
+NCU_TRAFFIC = {"gn_silu_bwd": 2 * (268_502_016 + 92_896_256), "gn_silu_fwd": 2 * (134_456_576 + 79_868_672),
                "ln_fwd": 2 * (134_267_904 + 83_640_064), "ln_bwd": 2 * (269_501_952 + 95_807_232)}
 
 

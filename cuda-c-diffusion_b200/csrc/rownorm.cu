@@ -488,10 +488,10 @@ void launch_layernorm_forward(float* y, float* mu, float* rstd, const float* x, 
         return;
     const long rows = batch;
     if (fast_rows_ok(C) && aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)) {
-        RN_DISPATCH_VPT(C, (launch_k(layernorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "ln_blocks_per_sm", 8),
+        RN_DISPATCH_VPT(C, (launch_k(layernorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "ln_blocks_per_sm", 64),
                                 RN_THREADS, 0, s, y, mu, rstd, x, gamma, beta, rows, eps)));
     } else {
-        launch_k(layernorm_fwd_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s,
+        launch_k(layernorm_fwd_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 64), RN_THREADS, 0, s,
             y, mu, rstd, x, gamma, beta, rows, C, eps);
     }
     count_launch();
@@ -507,7 +507,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
     Scratch sc;
     if (fast_rows_ok(C) && rows > 0 && aligned16(grad_in) && aligned16(grad_out) && aligned16(x) && aligned16(gamma)) {
         const int R = (C / 128 == 1) ? 4 : (C / 128 == 2 ? 2 : 1);
-        const int grid = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 4);
+        const int grid = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 2);
         B200_REQUIRE(scratch_get(s, (size_t)grid * 2 * C, 0, &sc), "layernorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
         RN_DISPATCH_VPT(C, (launch_k(layernorm_bwd_rows<VPT, R>, grid, RN_THREADS, 0, s, grad_in, sc.partials, grad_out, x,
                                 gamma, mu, rstd, rows)));
@@ -517,7 +517,7 @@ void launch_layernorm_backward(float* grad_in, float* ggamma, float* gbeta, cons
         return;
     }
     if (rows > 0) {
-        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s,
+        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 64), RN_THREADS, 0, s,
             grad_in, grad_out, x, gamma, mu, rstd, rows, C);
         count_launch();
         B200_CHECK_LAUNCH();
@@ -540,10 +540,10 @@ void launch_pixel_norm_forward(float* y, const float* x, int rows_i, int C, floa
         return;
     const long rows = rows_i;
     if (fast_rows_ok(C) && aligned16(y) && aligned16(x)) {
-        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
+        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_fwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 64),
                                 RN_THREADS, 0, s, y, x, rows, eps)));
     } else {
-        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s, y, nullptr, x,
+        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 64), RN_THREADS, 0, s, y, nullptr, x,
             rows, C, eps, 0);
     }
     count_launch();
@@ -558,10 +558,10 @@ void launch_pixel_norm_backward(float* dx, const float* dy, const float* x, int 
         return;
     const long rows = rows_i;
     if (fast_rows_ok(C) && aligned16(dx) && aligned16(dy) && aligned16(x)) {
-        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_bwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 8),
+        RN_DISPATCH_VPT(C, (launch_k(pixelnorm_bwd_rows<VPT, R>, rows_grid(rows, RN_WARPS * R, "pn_blocks_per_sm", 64),
                                 RN_THREADS, 0, s, dx, dy, x, rows, eps)));
     } else {
-        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 8), RN_THREADS, 0, s, dx, dy, x, rows,
+        launch_k(pixelnorm_generic, rows_grid(rows, RN_WARPS, "pn_blocks_per_sm", 64), RN_THREADS, 0, s, dx, dy, x, rows,
             C, eps, 1);
     }
     count_launch();
@@ -634,7 +634,7 @@ extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, 
     const int chunk_rows = 256;
     long nparts;
     if (fast) {
-        nparts = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 4);
+        nparts = rows_grid(rows, RN_WARPS * R, "ln_bwd_blocks_per_sm", 2);
         const long fit = (long)(LN_NOALLOC_MAX_FLOATS / (2 * (size_t)C));
         if (nparts > fit)
             nparts = fit;  // fewer, longer-running CTAs: the grid-stride loop covers all rows
@@ -670,7 +670,7 @@ extern "C" int launch_layernorm_backward_noalloc(float* grad_in, float* ggamma, 
         return cudaPeekAtLastError() == cudaSuccess ? 0 : -4;
     }
     if (rows > 0) {
-        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 8), RN_THREADS, 0, s, grad_in,
+        launch_k(layernorm_bwd_dx_generic, rows_grid(rows, RN_WARPS, "ln_blocks_per_sm", 64), RN_THREADS, 0, s, grad_in,
             grad_out, x, gamma, mu, rstd, rows, C);
         NOALLOC_LAUNCHED();
     }

@@ -43,13 +43,22 @@ def _free_bytes():
     return torch.cuda.mem_get_info()[0]  # cudaMemGetInfo: free bytes of the device, all allocators included
 
 
-# the last two pairs reach the limits of the fixed array: C = 1024 / 896 with enough rows that the grid (4 CTAs
-# per SM) has to be clipped to the partial rows that fit (2^20 / 2048 = 512 CTAs; the grid-stride loop covers
-# the rest), and the generic path (C not a multiple of 128) with ceil(rows/256) * 2*C just under 2^20 floats
+# the last two pairs reach the limits of the fixed array: C = 1024 / 896 with a grid (forced to 8 CTAs per SM
+# through the tunable) that has to be clipped to the partial rows that fit (2^20 / 2048 = 512 CTAs; the
+# grid-stride loop covers the rest), and the generic path (C not a multiple of 128) with
+# ceil(rows/256) * 2*C just under 2^20 floats
 @pytest.mark.parametrize("shapes", [[(3000, 256), (777, 256)], [(500, 100), (4100, 384)],
-                                    [(6000, 1024), (5000, 896)], [(256 * 2600, 200), (1000, 200)]])
+                                    [(12000, 1024), (10000, 896)], [(256 * 2600, 200), (1000, 200)]])
 def test_noalloc_backward_matches_regular_backward_twice_in_a_row(lib, shapes):
     keep = []
+    lib.b200_tune_set(b"ln_bwd_blocks_per_sm", 8 if shapes[0][1] == 1024 else 2)
+    try:
+        _noalloc_pairs(lib, shapes, keep)
+    finally:
+        lib.b200_tune_set(b"ln_bwd_blocks_per_sm", 2)
+
+
+def _noalloc_pairs(lib, shapes, keep):
     for i, (rows, C) in enumerate(shapes):
         # the regular entry point first: it (and torch) may allocate; what follows must not
         _, rdx, rdg, rdb = _run(lib, lib.launch_layernorm_backward, rows, C, 100 + i, keep)
