@@ -627,6 +627,16 @@ def edm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, gra
     return got
 
 
+def ddpm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, sharded=None):
+    """Data-parallel DDPM UNet training (build/bin/ddpm_dp_train: the reference's DDPM UNet with the residual block
+    on the fused GroupNorm+SiLU kernels, CUDA graph, NCCL); device-timed, max over ranks."""
+    args = ["--batch", str(batch_per_gpu), "--steps", str(steps), "--warmup", str(warmup), "--graph"]
+    if sharded:
+        args += ["--sharded", sharded]
+    return run_rank_program(BIN / "ddpm_dp_train", args, world, rank, local_rank, f"ddpm_dp_train_{batch_per_gpu}",
+                            "ddpm_dp_train", timeout=90)
+
+
 # ------------------------------------------------------------------------------------ main
 KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd": 2 * NEL * 4, "ln_bwd": 3 * NEL * 4,
                 "sinusoidal": B * EMB * 4}
@@ -776,6 +786,13 @@ def main():
         else:
             dp["weak_256_per_gpu_reference_conv2d"] = edm_dp_train(world, rank, local, 256, fastconv=False)
         line["edm_dp_train"] = dp
+        if world > 1:
+            torch.distributed.barrier()
+        ddp = {"weak_256_per_gpu": ddpm_dp_train(world, rank, local, 256)}
+        if world > 1:
+            torch.distributed.barrier()
+            ddp["strong_256_global"] = ddpm_dp_train(world, rank, local, 256 // world)
+        line["ddpm_dp_train"] = ddp
     if rank == 0:
         if not args.no_cpu and (world == 1 or args.impl == "reference"):
             line["cpu_baseline"] = cpu_baseline()

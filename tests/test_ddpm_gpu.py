@@ -145,3 +145,63 @@ def test_ddpm_block_gradients_by_central_differences():
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "0 failure(s)" in res.stdout and res.stdout.count("PASS") == 3 * 12 and "FAIL" not in res.stdout
+
+
+def test_ddpm_dp_step_matches_reference_step():
+    """csrc/host/ddpm_dp_train.c --check: the batched data-parallel step (one launch for the forward diffusion,
+    one for the min-SNR-weighted loss gradient, pinned uploads) against the reference's own ddpm_loss_step on the
+    same model from the same host and device random state: same loss, same gradients."""
+    _need(BIN / "ddpm_dp_train")
+    res = subprocess.run([str(BIN / "ddpm_dp_train"), "--check"], capture_output=True, text=True, timeout=600)
+    print(res.stdout[-2000:])
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "0 failure(s)" in res.stdout and res.stdout.count("PASS") == 2
+
+
+def _dp_dump(tmp_path, name, extra, world=1):
+    import os
+    exe = BIN / "ddpm_dp_train"
+    dump = tmp_path / f"{name}.bin"
+    args = [str(exe), "--fp32", "--steps", "3", "--warmup", "2", "--batch", "16", "--dump", str(dump), *extra]
+    if world == 1:
+        res = subprocess.run(args, capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        out = res.stdout
+    else:
+        procs = []
+        for r in range(world):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), NCCL_NVLS_ENABLE="0")
+            procs.append(subprocess.Popen(args + ["--id-file", str(tmp_path / f"{name}.id")], env=env,
+                                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+        outs = [p.communicate(timeout=180) for p in procs]
+        assert all(p.returncode == 0 for p in procs), outs
+        out = outs[0][0]
+    import json
+    got = json.loads(next(ln for ln in out.splitlines() if ln.startswith("{")))["ddpm_dp_train"]
+    return np.fromfile(dump, dtype=np.float32), got
+
+
+def test_ddpm_dp_trainer_graph_and_sharded_optimizer_agree_with_eager(tmp_path):
+    """Five fp32 steps: eager, replayed from a CUDA graph, and with the range-sharded optimizer (world = 1) end
+    in the same parameters."""
+    _need(BIN / "ddpm_dp_train")
+    a, ga = _dp_dump(tmp_path, "eager", [])
+    b, gb = _dp_dump(tmp_path, "graph", ["--graph"])
+    c, gc = _dp_dump(tmp_path, "sharded", ["--sharded", "allgather"])
+    assert a.size > 900_000 and ga["replicas_in_sync"] and gb["cuda_graph_nodes"] > 100
+    assert np.isfinite(a).all() and np.isfinite(ga["last_loss"])
+    assert np.array_equal(a, b)
+    assert np.abs(a[1:] - c[1:]).max() <= 1e-6 * np.abs(a[1:]).max()
+
+
+def test_ddpm_dp_trainer_two_ranks(tmp_path):
+    """2 GPUs: replicas stay in sync with the all-reduce and with the sharded optimizer's peer stores, and both
+    end in the same parameters up to the order of the gradient sums."""
+    import torch
+    _need(BIN / "ddpm_dp_train")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    a, ga = _dp_dump(tmp_path, "replicated", ["--graph"], world=2)
+    b, gb = _dp_dump(tmp_path, "sharded", ["--graph", "--sharded", "peer"], world=2)
+    assert ga["replicas_in_sync"] and gb["replicas_in_sync"] and ga["n_gpus"] == 2
+    assert np.abs(a[1:] - b[1:]).max() <= 5e-5 * np.abs(a[1:]).max()
