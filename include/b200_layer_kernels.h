@@ -315,7 +315,8 @@ void b200_set_error_mode(int mode);
 int b200_error_count(void);
 int b200_last_error(char* buf, int buflen); /* copies the last message; returns its length */
 void b200_clear_error(void);
-/* Non-zero if a kernel's bounded wait ran out (synchronises the device). */
+/* Error word that a kernel sets when a bounded device-side wait runs out (synchronises the device).  No kernel
+   of the current library waits on another CTA, kernel or rank, so this reads 0; kept for hosts that poll it. */
 int b200_device_error_status(void);
 
 /* Number of kernels this library has launched since load (or since reset). */

@@ -183,14 +183,14 @@ def test_strip_and_generic_groupnorm_agree(lib, orc):
     """The generic kernels (any shape and alignment) on a shape the register strips normally take."""
     p = dict(B=4, HW=196, C=64, G=32, act="silu")
     inp = cases.make_inputs("groupnorm", p, seed=21)
-    tile = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    strips = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     lib.b200_tune_set(b"gn_force_generic", 1)
     try:
         gen = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
         lib.b200_tune_set(b"gn_force_generic", 0)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
-    _check(tile, ref, "strips")
+    _check(strips, ref, "strips")
     _check(gen, ref, "generic")
 
 
