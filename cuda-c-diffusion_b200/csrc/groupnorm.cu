@@ -4,9 +4,11 @@
 // x is viewed as a matrix [B*HW, C]; a work item is (sample b, Ct channels covering whole groups).
 // Three kernel families, tried in this order by gn_forward / gn_backward:
 //
-//   1. register-resident strips (groupnorm_strip.cuh, groupnorm_dstrip.cuh): the default.  A CTA keeps
-//      all HW rows of an item in registers, statistics and output come from registers, the next item
-//      is staged with cp.async while the current one is processed.  x (and dy) cross HBM exactly once.
+//   1. register-resident strips (groupnorm_strip.cuh, groupnorm_dstrip.cuh, groupnorm_ostrip.cuh): the
+//      default.  A CTA keeps all HW rows of an item in registers, statistics and output come from
+//      registers, the next item is staged with cp.async while the current one is processed.  x (and dy)
+//      cross HBM exactly once.  Launches with many strips per CTA take the one-barrier kernels of
+//      groupnorm_ostrip.cuh (forward in clusters of 4 CTAs whose staging bursts are kept in step).
 //   2. chunked strips (groupnorm_cstrip.cuh): samples too tall for the register file; the strip is
 //      walked twice in chunks, the second read coming from L2 while the strips in flight fit there.
 //   3. generic kernels (this file): any shape, any alignment (C % 4 != 0, misaligned pointers) and the
@@ -29,14 +31,27 @@
 #include "dev_common.cuh"
 #include "../../include/b200_layer_kernels.h"
 
+#include <atomic>
+
 namespace b200 {
 
 constexpr int GN_GENERIC_THREADS = 256;
+
+// launches per kernel family, for tests that must know which family they exercised (b200_groupnorm_path_count)
+enum : int { GN_PATH_STRIP = 0, GN_PATH_PIPELINED, GN_PATH_DEEP, GN_PATH_ONE_BARRIER, GN_PATH_CHUNKED, GN_PATH_GENERIC, GN_PATHS };
+static std::atomic<long long> g_gn_path[GN_PATHS];
+static inline bool gn_path(int path, bool launched)
+{
+    if (launched)
+        g_gn_path[path].fetch_add(1, std::memory_order_relaxed);
+    return launched;
+}
 
 }  // namespace b200
 
 #include "groupnorm_strip.cuh"
 #include "groupnorm_dstrip.cuh"
+#include "groupnorm_ostrip.cuh"
 #include "groupnorm_cstrip.cuh"
 
 namespace b200 {
@@ -237,17 +252,43 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
     return true;
 }
 
+// Cluster width for the next strip launch of this thread (1 = no cluster); with a width above 1 the grid is
+// cut to the clusters the device can hold at once (the kernels are persistent: fewer CTAs walk more strips).
+static thread_local int t_gn_cluster = 1;
+struct ClusterScope {
+    explicit ClusterScope(int w) { t_gn_cluster = w; }
+    ~ClusterScope() { t_gn_cluster = 1; }
+};
+
 template <class... KArgs, class... Args>
-static bool strip_launch(void (*kernel)(KArgs...), long grid, int NT, size_t smem, cudaStream_t s, Args... args)
+static bool strip_launch(int path, void (*kernel)(KArgs...), long grid, int NT, size_t smem, cudaStream_t s, Args... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3((unsigned)NT, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     unsigned nat = 0;
     pdl_attribute(at, &nat);
+    if (t_gn_cluster > 1) {
+        const int w = t_gn_cluster;
+        at[nat].id = cudaLaunchAttributeClusterDimension;
+        at[nat].val.clusterDim.x = (unsigned)w;
+        at[nat].val.clusterDim.y = 1;
+        at[nat].val.clusterDim.z = 1;
+        ++nat;
+        cfg.attrs = at;
+        cfg.numAttrs = nat;
+        cfg.gridDim.x = (unsigned)((grid + w - 1) / w * w);
+        int nclusters = 0;
+        if (cfg.gridDim.x == 0 || cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess || nclusters < 1) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        if ((long)nclusters * w < (long)cfg.gridDim.x)
+            cfg.gridDim.x = (unsigned)(nclusters * w);
+    }
     cfg.attrs = at;
     cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
@@ -257,11 +298,11 @@ static bool strip_launch(void (*kernel)(KArgs...), long grid, int NT, size_t sme
         return false;
     }
     count_launch();
-    return true;
+    return gn_path(path, true);
 }
 
 template <class... KArgs, class... Args>
-static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, int NT, size_t smem, cudaStream_t s,
+static bool pstrip_launch(int path, void (*kernel)(KArgs...), bool* attr_done, long grid, int NT, size_t smem, cudaStream_t s,
     Args... args)
 {
     int dev = 0;
@@ -278,7 +319,7 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
         }
         attr_done[dev] = true;
     }
-    return strip_launch(kernel, grid, NT, smem, s, args...);
+    return strip_launch(path, kernel, grid, NT, smem, s, args...);
 }
 
 #define PSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
@@ -286,16 +327,16 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
         static bool done[64] = { false };                                                                   \
         if (full) {                                                                                         \
             static bool donef[64] = { false };                                                              \
-            return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, psmem, s, y, mu, rstd, x, \
+            return pstrip_launch(GN_PATH_PIPELINED, gn_fwd_pstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, psmem, s, y, mu, rstd, x, \
                 gamma, beta, plan.g, eps, (int)grid);                                                       \
         }                                                                                                   \
-        return pstrip_launch(gn_fwd_pstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, psmem, s, y, mu, rstd, x, \
+        return pstrip_launch(GN_PATH_PIPELINED, gn_fwd_pstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, psmem, s, y, mu, rstd, x, \
             gamma, beta, plan.g, eps, (int)grid);                                                           \
     }
 #define PSTRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
         static bool done[64] = { false };                                                                   \
-        return pstrip_launch(gn_bwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, dx, sc.partials,       \
+        return pstrip_launch(GN_PATH_PIPELINED, gn_bwd_pstrip<NTv, VPTv, ACT, MBv>, done, pgrid, NTv, psmem, s, dx, sc.partials,       \
                    dy, x, gamma, beta, mu, rstd, plan.g, (int)grid)                                   \
             && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);            \
     }
@@ -306,10 +347,10 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
         static bool done[64] = { false };                                                                   \
         if (full) {                                                                                         \
             static bool donef[64] = { false };                                                              \
-            return pstrip_launch(gn_fwd_dstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
+            return pstrip_launch(GN_PATH_DEEP, gn_fwd_dstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
                 gamma, beta, plan.g, eps, (int)grid);                                                       \
         }                                                                                                   \
-        return pstrip_launch(gn_fwd_dstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
+        return pstrip_launch(GN_PATH_DEEP, gn_fwd_dstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
             gamma, beta, plan.g, eps, (int)grid);                                                           \
     }
 #define DSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
@@ -317,20 +358,66 @@ static bool pstrip_launch(void (*kernel)(KArgs...), bool* attr_done, long grid, 
         static bool done[64] = { false };                                                                   \
         static bool donef[64] = { false };                                                                  \
         const bool ok = full                                                                                \
-            ? pstrip_launch(gn_bwd_dstrip<NTv, VPTv, ACT, true>, donef, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
+            ? pstrip_launch(GN_PATH_DEEP, gn_bwd_dstrip<NTv, VPTv, ACT, true>, donef, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
                   gamma, beta, mu, rstd, plan.g, (int)grid)                                           \
-            : pstrip_launch(gn_bwd_dstrip<NTv, VPTv, ACT, false>, done, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
+            : pstrip_launch(GN_PATH_DEEP, gn_bwd_dstrip<NTv, VPTv, ACT, false>, done, pgrid, NTv, dsmem, s, dx, sc.partials, dy, x,  \
                   gamma, beta, mu, rstd, plan.g, (int)grid);                                          \
         return ok && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);      \
     }
 
+// one-barrier strips (groupnorm_ostrip.cuh): groups per float4 column the kernels are built for, 0 = not eligible
+static int ostrip_gpt(const StripGeom& g)
+{
+    if (g.Q > 32 || (g.Q & (g.Q - 1)) != 0 || g.C > 2048)
+        return 0;
+    if (g.cpg == 2)
+        return 2;
+    if (g.cpg % 4 == 0 && ((g.cpg / 4) & (g.cpg / 4 - 1)) == 0)
+        return 1;
+    return 0;
+}
+
+template <int NT, int VPT, int ACT, int MB, class... Args>
+static bool ostrip_fwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaStream_t s, Args... args)
+{
+    static bool done[4][64] = {};
+    if (full)
+        return gpt == 1
+            ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_fwd_ostrip<NT, VPT, ACT, MB, true, 1>, done[0], pgrid, NT, smem, s, args...)
+            : pstrip_launch(GN_PATH_ONE_BARRIER, gn_fwd_ostrip<NT, VPT, ACT, MB, true, 2>, done[1], pgrid, NT, smem, s, args...);
+    return gpt == 1
+        ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_fwd_ostrip<NT, VPT, ACT, MB, false, 1>, done[2], pgrid, NT, smem, s, args...)
+        : pstrip_launch(GN_PATH_ONE_BARRIER, gn_fwd_ostrip<NT, VPT, ACT, MB, false, 2>, done[3], pgrid, NT, smem, s, args...);
+}
+
+template <int NT, int VPT, int ACT, class... Args>
+static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaStream_t s, Args... args)
+{
+    static bool done[4][64] = {};
+    if (full)
+        return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 1>, done[0], pgrid, NT, smem, s, args...)
+                        : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 2>, done[1], pgrid, NT, smem, s, args...);
+    return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 1>, done[2], pgrid, NT, smem, s, args...)
+                    : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 2>, done[3], pgrid, NT, smem, s, args...);
+}
+
+#define OSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
+    if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv)                                                \
+        return ostrip_fwd_launch<NTv, VPTv, ACT, MBv>(full, gpt, pgrid, osmem, s, y, mu, rstd, x, gamma, beta, plan.g, \
+            eps, (int)grid);
+#define OSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
+    if (plan.NT == NTv && plan.VPT == VPTv)                                                                 \
+        return ostrip_bwd_launch<NTv, VPTv, ACT>(full, gpt, pgrid, osmem, s, dx, sc.partials, dy, x, gamma, beta, mu,  \
+                   rstd, plan.g, (int)grid)                                                                 \
+            && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
+
 #define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
-        return strip_launch(gn_fwd_strip<NTv, VPTv, ACT>, grid, NTv, plan.smem, s, y, mu, rstd, x, gamma, \
+        return strip_launch(GN_PATH_STRIP, gn_fwd_strip<NTv, VPTv, ACT>, grid, NTv, plan.smem, s, y, mu, rstd, x, gamma, \
             beta, plan.g, eps);
 #define STRIP_BWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                \
-        return strip_launch(gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, plan.smem, s, dx, sc.partials,      \
+        return strip_launch(GN_PATH_STRIP, gn_bwd_strip<NTv, VPTv, ACT, MBv>, grid, NTv, plan.smem, s, dx, sc.partials,      \
                    dy, x, gamma, beta, mu, rstd, plan.g, B)                                          \
             && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
 
@@ -378,6 +465,19 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 // deep staging: half a strip more in flight, in the shared memory the plain pipeline leaves unused
                 const size_t dsmem = (size_t)(plan.VPT + plan.VPT / 2) * plan.NT * 16 + plan.smem;
                 // (measured on [256,32,32,256]: 2 % slower than the plain pipeline in forward, so off unless asked for)
+                // one barrier per strip
+                const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
+                const size_t osmem = (size_t)plan.VPT * plan.NT * 16
+                    + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * (plan.NT / 32) + 4)) * sizeof(float);
+                // (with few strips per CTA the longer set-up of these kernels costs more than the barriers save)
+                if (gpt && osmem * per_sm <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min_fwd", 3)) {
+                    // clusters of 4 neighbouring strips, staged in step (see gn_fwd_ostrip)
+                    const int cw = tune_get("gn_fwd_cluster", 4);
+                    const bool clustered = cw > 1 && per_sm == 1 && full && plan.g.nct % cw == 0 && per_cta >= 8;
+                    ClusterScope cluster(clustered ? cw : 1);
+                    OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
+                    OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
+                }
                 if (tune_get("gn_deep_fwd", 0) && dsmem * per_sm <= 226 * 1024 && grid >= 3 * pgrid) {
                     DSTRIP_FWD_CASE(1024, 4, 1) DSTRIP_FWD_CASE(1024, 8, 1)
                     DSTRIP_FWD_CASE(512, 4, 2) DSTRIP_FWD_CASE(512, 8, 2) DSTRIP_FWD_CASE(512, 8, 1)
@@ -436,6 +536,16 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                 const size_t dsmem = (size_t)3 * plan.VPT * plan.NT * 16 + plan.smem;
                 // (2 % faster than the plain pipeline when every CTA walks many strips; with only a few strips per
                 // CTA the longer prologue costs more than the deeper staging gains)
+                const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
+                const int nw = plan.NT / 32;
+                const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
+                    + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * nw + 4)) * sizeof(float)
+                    + (size_t)2 * nw * 2 * plan.g.Q * 16;
+                // (a cluster barrier per strip, as in the forward kernel, was measured here too: 0.89 -> 0.78 with
+                // pairs, worse with wider clusters -- the backward has no idle time to absorb the lock step)
+                if (gpt && per_sm == 1 && osmem <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min", 8)) {
+                    OSTRIP_BWD_CASE(1024, 4) OSTRIP_BWD_CASE(512, 4) OSTRIP_BWD_CASE(512, 8)
+                }
                 if (tune_get("gn_deep", 1) && per_sm == 1 && dsmem <= 226 * 1024 && grid >= 8 * pgrid) {
                     DSTRIP_BWD_CASE(1024, 4) DSTRIP_BWD_CASE(512, 4) DSTRIP_BWD_CASE(512, 8)
                 }
@@ -504,9 +614,9 @@ static bool gn_forward_cstrip(float* y, float* mu, float* rstd, const float* x, 
         const size_t psmem = (size_t)VPT * plan.NT * 16 + plan.smem;
         static bool done4[64] = { false }, done8[64] = { false };
         if (VPT == 8)
-            return pstrip_launch(gn_fwd_cstrip<512, 8, ACT, MB>, done8, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
+            return pstrip_launch(GN_PATH_CHUNKED, gn_fwd_cstrip<512, 8, ACT, MB>, done8, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
                 plan.g, eps, (int)items, nchunks);
-        return pstrip_launch(gn_fwd_cstrip<512, 4, ACT, MB>, done4, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
+        return pstrip_launch(GN_PATH_CHUNKED, gn_fwd_cstrip<512, 4, ACT, MB>, done4, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
             plan.g, eps, (int)items, nchunks);
     }
 }
@@ -542,9 +652,9 @@ static bool gn_backward_cstrip(float* dx, float* dgamma, float* dbeta, const flo
         const size_t psmem = (size_t)2 * VPT * plan.NT * 16 + plan.smem;
         static bool done4[64] = { false }, done8[64] = { false };
         const bool ok = VPT == 4
-            ? pstrip_launch(gn_bwd_cstrip<512, 4, ACT, 2>, done4, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
+            ? pstrip_launch(GN_PATH_CHUNKED, gn_bwd_cstrip<512, 4, ACT, 2>, done4, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
                   mu, rstd, plan.g, (int)items, nchunks)
-            : pstrip_launch(gn_bwd_cstrip<512, 8, ACT, 1>, done8, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
+            : pstrip_launch(GN_PATH_CHUNKED, gn_bwd_cstrip<512, 8, ACT, 1>, done8, pgrid, 512, psmem, s, dx, sc.partials, dy, x, gamma, beta,
                   mu, rstd, plan.g, (int)items, nchunks);
         return ok && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
     }
@@ -558,6 +668,7 @@ static void gn_forward(float* y, float* mu, float* rstd, const float* x, const f
         return;
     if (gn_forward_cstrip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
+    gn_path(GN_PATH_GENERIC, true);
     launch_k(gn_fwd_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, y, mu, rstd, x, gamma, beta, HW, C, G, eps);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -575,6 +686,7 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     Scratch sc;
     B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
     B200_REQUIRE(B <= 65535, "groupnorm_backward: batch %d too large for the generic path", B);
+    gn_path(GN_PATH_GENERIC, true);
     launch_k(gn_bwd_dx_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
     count_launch();
     B200_CHECK_LAUNCH();
@@ -647,6 +759,11 @@ void launch_groupnorm_act_backward(float* dx, float* ggamma, float* gbeta, const
     if (!gn_args_ok("groupnorm_act_backward", batch, HW, C, G) || batch == 0)
         return;
     GN_DISPATCH_ACT((int)act, (gn_backward<A>(dx, ggamma, gbeta, dy, x, gamma, beta, mu, rstd, batch, HW, C, G, s)));
+}
+
+long long b200_groupnorm_path_count(int path)
+{
+    return path >= 0 && path < b200::GN_PATHS ? b200::g_gn_path[path].load(std::memory_order_relaxed) : -1;
 }
 
 }  // extern "C"

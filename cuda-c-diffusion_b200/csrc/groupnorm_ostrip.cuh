@@ -1,0 +1,513 @@
+// One-barrier GroupNorm strip kernels (included by groupnorm.cu after groupnorm_dstrip.cuh).
+//
+// The pipelined strips of groupnorm_strip.cuh / groupnorm_dstrip.cuh cross three CTA barriers per
+// strip, and between them a handful of threads works while the rest of the SM waits: Ct threads add
+// the per-warp channel sums, then Gt threads turn channel sums into group statistics (with global
+// loads of gamma, of the shift row or of mu/rstd on that path).  With one 512- or 1024-thread CTA per
+// SM nothing else can run during those sections, so they are pure latency on every strip.
+//
+// Here a strip crosses ONE barrier:
+//   * the sums that the second phase needs are reduced to GROUP level inside each warp (xor shuffles
+//     over the lanes that share a group), one float2 per (warp, group) goes to shared memory, and after
+//     the barrier every warp forms the totals of its own groups: the lanes that share a group split the NW
+//     per-warp values between them and combine with the same shuffles -- no elected threads, no second
+//     and third barrier, a fixed order of additions (results are bit-reproducible);
+//   * the reduction buffers alternate with the strip parity, which is what makes the single barrier
+//     sufficient (a buffer is rewritten two strips later, after every thread has passed the barrier
+//     in between);
+//   * everything a strip needs from global memory besides the strip itself arrives through the
+//     staging pipeline, in slots owned by the thread that reads them: the shift of the forward pass
+//     (row 0 of the group's first channel) and mu/rstd of the backward pass (which come from DRAM, a
+//     microsecond away); gamma and beta of all C channels are copied to shared memory once per CTA;
+//   * the backward's per-channel sums (dgamma/dbeta partial rows) are still written per warp, but they
+//     are added up by Ct threads AFTER those threads have issued their dx stores: off the critical path.
+//
+// Measured on [256,32,32,256] with SiLU, each kernel alone in a loop (fraction of the copy rate): backward
+// 0.83 -> 0.88 (0.86 -> 0.97 without activation); forward 0.86 -> 0.78 as plain CTAs, 0.90 in clusters of
+// 4 (see gn_fwd_ostrip).  With only a few strips per CTA the longer set-up loses, so the dispatcher keeps
+// the three-barrier kernels for such launches.
+//
+// Forward statistics use one shift per GROUP (the group's first channel in row 0) instead of one per
+// channel: mean = K + S1/n, var = S2/n - (S1/n)^2 with S1, S2 the sums of (x - K) and (x - K)^2.  S1 can be
+// as large as n * |K - mean|, so its cross-warp total is carried as an unevaluated pair of floats and the
+// division keeps the remainder: the mean loses nothing to the size of the shift.
+//
+// Applies when a thread's float4 lies in one group (cpg a multiple of 4, cpg/4 a power of two: GPT = 1)
+// or in exactly two (cpg = 2: GPT = 2), Q = Ct/4 is a power of two <= 32 and C <= 2048.
+#pragma once
+
+namespace b200 {
+
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// Lanes of a warp that share a group: Lg of them, this lane being number li (the same numbering in every
+// warp, so every warp derives bit-identical totals from the same partials).
+struct OStripLanes {
+    int li, Lg;
+};
+template <int GPT>
+__device__ __forceinline__ OStripLanes ostrip_lanes(int lane, int q, int Q, int M)
+{
+    OStripLanes r;
+    if (GPT == 1) {
+        r.Lg = M * (32 / Q);
+        r.li = (q & (M - 1)) + M * (lane / Q);
+    } else {
+        r.Lg = 32 / Q;
+        r.li = lane / Q;
+    }
+    return r;
+}
+
+// a + b as an unevaluated pair (sum, rounding error): Knuth's two-sum, symmetric in its arguments.
+__device__ __forceinline__ void two_sum(float a, float b, float& s, float& e)
+{
+    s = a + b;
+    const float bb = s - a;
+    e = (a - (s - bb)) + (b - bb);
+}
+
+// Total over the NW per-warp float2 partials of one group after the barrier: each of the group's Lg lanes adds
+// the partials li, li + Lg, ..., then the lanes combine over the same xor offsets that formed the partials.
+// The first component is carried as (hi, lo): in the forward pass it is a sum of n shifted values whose
+// magnitude n * |shift - mean| would otherwise cost the mean its last digits.
+template <int NW, bool PAIR>
+__device__ __forceinline__ void ostrip_group_total(const float* rg, const OStripLanes ln, int Q, int M, float& hi, float& lo,
+    float& second)
+{
+    float h = 0.0f, l = 0.0f, b = 0.0f;
+    for (int i = ln.li; i < NW; i += ln.Lg) {
+        const float2 p = *reinterpret_cast<const float2*>(rg + 2 * i);
+        if (PAIR) {
+            float e;
+            two_sum(h, p.x, h, e);
+            l += e;
+        } else {
+            h += p.x;
+        }
+        b += p.y;
+    }
+    auto step = [&](int off) {
+        const float h2 = __shfl_xor_sync(0xffffffffu, h, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+        if (PAIR) {
+            const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+            float e;
+            two_sum(h, h2, h, e);
+            l = (l + l2) + e;
+        } else {
+            h += h2;
+        }
+    };
+    for (int off = 1; off < M; off <<= 1)
+        step(off);
+    for (int off = Q; off < 32; off <<= 1)
+        step(off);
+    hi = h;
+    lo = l;
+    second = b;
+}
+
+// ---------------------------------------------------------------------------
+// forward: one strip staged ahead (staging a second strip half ahead, as gn_fwd_dstrip does, measured 3 % slower
+// with and without clusters).
+// dynamic smem = stage[VPT][NT] float4 | kst[GPT][NT] | gamma[C] | beta[C] | redg[2][Gt][2*NW+4]
+//
+// Launched as clusters of 4 CTAs where that applies (1024-thread CTAs, many strips each, strips per sample a
+// multiple of 4): consecutive CTAs walk consecutive strips, i.e. neighbouring 128-byte column tiles of the SAME
+// rows, and a cluster barrier in front of every staging burst makes the four bursts (and later the four store
+// phases) coincide, so that DRAM sees 512 contiguous bytes per row at once instead of four isolated 128-byte
+// accesses at different times.  Measured on [256,32,32,256]: 0.78 -> 0.90 of the copy rate, although only 132
+// of the 148 SMs can hold a cluster of 4 at one CTA per SM; widths 2 (0.85) and 8 (0.83, 120 SMs) lose.
+// ---------------------------------------------------------------------------
+template <int NT, int VPT, int ACT, int MB, bool FULL, int GPT>
+__global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, float* __restrict__ mu,
+    float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
+{
+    pdl_prologue();
+    constexpr int NW = NT / 32;
+    constexpr int RG = 2 * NW + 4;  // floats per group row (16 bytes of padding: rows of different groups on different banks)
+    extern __shared__ float4 strip_stage[];
+    float4* stage = strip_stage;
+    float* kst = reinterpret_cast<float*>(stage + VPT * NT);  // slot [k][t]: shift of this thread's group k
+    float* gsm = kst + GPT * NT;
+    float* bsm = gsm + g.C;
+    float* redg = bsm + g.C;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int q = t % g.Q, rl = t / g.Q;
+    const int cb = 4 * q;
+    const int M = GPT == 1 ? (g.cpg >> 2) : 1;       // lanes (float4 columns) per group
+    const int gl = GPT == 1 ? q / M : 2 * q;          // this thread's (first) group within the strip
+    const int koff = gl * g.cpg;                      // first channel of that group: row 0 of it is the shift
+    const OStripLanes ln = ostrip_lanes<GPT>(lane, q, g.Q, M);
+    const float nf = (float)g.HW * (float)g.cpg;
+    const bool writer = lane < g.Q && (GPT == 2 || (lane & (M - 1)) == 0);
+    const float inv_n = 1.0f / nf;
+    const size_t rowoff = (size_t)rl * g.C + cb;
+    const size_t jstride = (size_t)g.RSTEP * g.C;
+    const int G = gridDim.x;
+
+    for (int i = t; i < g.C / 4; i += NT) {
+        reinterpret_cast<float4*>(gsm)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+        reinterpret_cast<float4*>(bsm)[i] = __ldg(reinterpret_cast<const float4*>(beta) + i);
+    }
+    // asynchronous copies of work item `it` into the staging slots of this thread (and its shift slots)
+    auto stage_item = [&](int it) {
+        const size_t sb = dstrip_item_offset(g, it, 0);
+#pragma unroll
+        for (int k = 0; k < GPT; ++k)
+            cp_async4(&kst[k * NT + t], x + sb + koff + k * g.cpg);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+            if (FULL || rl + j * g.RSTEP < g.HW)
+                cp_async16(&stage[j * NT + t], x + sb + rowoff + j * jstride);
+    };
+    int item = blockIdx.x;
+    if (item < nitems)
+        stage_item(item);
+    cp_async_commit();
+    __syncthreads();  // gamma / beta staged
+    // CTAs of a cluster walk neighbouring strips of the same rows; a cluster barrier before each staging burst
+    // keeps their requests for one DRAM page together.  Only when every CTA of a cluster runs the same number of
+    // iterations (grid and item count multiples of the cluster width), else no CTA touches the barrier.
+    unsigned csize;
+    asm("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
+    const bool csync = csize > 1 && G % (int)csize == 0 && nitems % (int)csize == 0;
+
+    int par = 0;
+    for (; item < nitems; item += G, par ^= 1) {
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const size_t base = (size_t)b * g.HW * g.C + c0;
+        cp_async_wait_all();
+        if (csync)  // arrive now, wait after the shared-memory reads: the barrier's latency hides behind them
+            asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        const float k0 = kst[t], k1 = kst[(GPT - 1) * NT + t];
+        float4 v[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            v[j] = stage[j * NT + t];
+            if (!FULL && rl + j * g.RSTEP >= g.HW)
+                v[j] = make_float4(k0, k0, k1, k1);  // contributes zero to the shifted sums
+        }
+        if (csync)
+            asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        if (item + G < nitems)
+            stage_item(item + G);
+        cp_async_commit();
+
+        float S1[GPT], S2[GPT];
+        {
+            const f32x2 nk01 = pk1(-k0), nk23 = pk1(-k1);
+            f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const f32x2 d01 = pk_add(pk(v[j].x, v[j].y), nk01), d23 = pk_add(pk(v[j].z, v[j].w), nk23);
+                a1 = pk_add(a1, d01);
+                b1 = pk_add(b1, d23);
+                a2 = pk_fma(d01, d01, a2);
+                b2 = pk_fma(d23, d23, b2);
+            }
+            float a1l, a1h, b1l, b1h, a2l, a2h, b2l, b2h;
+            unpk(a1, a1l, a1h);
+            unpk(b1, b1l, b1h);
+            unpk(a2, a2l, a2h);
+            unpk(b2, b2l, b2h);
+            if constexpr (GPT == 1) {
+                S1[0] = (a1l + a1h) + (b1l + b1h);
+                S2[0] = (a2l + a2h) + (b2l + b2h);
+            } else {
+                S1[0] = a1l + a1h; S1[1] = b1l + b1h;
+                S2[0] = a2l + a2h; S2[1] = b2l + b2h;
+            }
+        }
+        // lanes of one group within the warp: the row lanes (offsets Q .. 16) and, for GPT = 1, the M
+        // neighbouring float4 columns (offsets 1 .. M/2)
+        for (int off = g.Q; off < 32; off <<= 1) {
+#pragma unroll
+            for (int k = 0; k < GPT; ++k) {
+                S1[k] += __shfl_xor_sync(0xffffffffu, S1[k], off);
+                S2[k] += __shfl_xor_sync(0xffffffffu, S2[k], off);
+            }
+        }
+        if constexpr (GPT == 1) {
+            for (int off = 1; off < M; off <<= 1) {
+                S1[0] += __shfl_xor_sync(0xffffffffu, S1[0], off);
+                S2[0] += __shfl_xor_sync(0xffffffffu, S2[0], off);
+            }
+        }
+        float* rg = redg + par * g.Gt * RG;
+        if (writer) {
+#pragma unroll
+            for (int k = 0; k < GPT; ++k)
+                *reinterpret_cast<float2*>(rg + (gl + k) * RG + 2 * warp) = make_float2(S1[k], S2[k]);
+        }
+        __syncthreads();
+
+        float mean[GPT], rs[GPT];
+#pragma unroll
+        for (int k = 0; k < GPT; ++k) {
+            float hi, lo, s2;
+            ostrip_group_total<NW, true>(rg + (gl + k) * RG, ln, g.Q, M, hi, lo, s2);
+            // S1 / n to full precision: quotient of the leading part, exact remainder, then the tail
+            const float qh = hi * inv_n;
+            const float rem = (fmaf(-qh, nf, hi) + lo) * inv_n;
+            const float m1 = qh + rem;
+            const float var = fmaxf(fmaf(-m1, m1, s2 * inv_n), 0.0f);
+            rs[k] = rsqrtf(var + eps);
+            mean[k] = ((k == 0 ? k0 : k1) + qh) + rem;
+        }
+        if (warp == 0 && writer) {
+            const int gi = b * g.G + c0 / g.cpg + gl;
+#pragma unroll
+            for (int k = 0; k < GPT; ++k) {
+                mu[gi + k] = mean[k];
+                rstd[gi + k] = rs[k];
+            }
+        }
+        const float4 ga = *reinterpret_cast<const float4*>(gsm + c0 + cb);
+        const float4 be = *reinterpret_cast<const float4*>(bsm + c0 + cb);
+        const float rs0 = rs[0], rs1 = rs[GPT - 1], mean0 = mean[0], mean1 = mean[GPT - 1];
+        float4 sc, sh;
+        sc.x = ga.x * rs0; sh.x = be.x - mean0 * sc.x;
+        sc.y = ga.y * rs0; sh.y = be.y - mean0 * sc.y;
+        sc.z = ga.z * rs1; sh.z = be.z - mean1 * sc.z;
+        sc.w = ga.w * rs1; sh.w = be.w - mean1 * sc.w;
+        const f32x2 sc01 = pk(sc.x, sc.y), sc23 = pk(sc.z, sc.w), sh01 = pk(sh.x, sh.y), sh23 = pk(sh.z, sh.w);
+        float* yrow = y + base + rowoff;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (FULL || rl + j * g.RSTEP < g.HW) {
+                float4 o;
+                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].x, v[j].y), sc01, sh01)), o.x, o.y);
+                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].z, v[j].w), sc23, sh23)), o.z, o.w);
+                __stcs(reinterpret_cast<float4*>(yrow + j * jstride), o);
+            }
+        }
+    }
+    cp_async_wait_all();
+}
+
+// ---------------------------------------------------------------------------
+// backward (deep-staged: x double-buffered, dy single-buffered, as in gn_bwd_dstrip).
+// dynamic smem = xs[2][VPT][NT] float4 | ds[VPT][NT] float4 | mst[2*GPT][NT] | gamma[C] | beta[C]
+//              | redg[2][Gt][2*NW+4] | redc[2][NW][2][Q] float4
+// ---------------------------------------------------------------------------
+template <int NT, int VPT, int ACT, bool FULL, int GPT>
+__global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, float* __restrict__ partials,
+    const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
+    const int nitems)
+{
+    pdl_prologue();
+    constexpr int NW = NT / 32;
+    constexpr int RG = 2 * NW + 4;
+    extern __shared__ float4 strip_stage[];
+    float4* xs = strip_stage;
+    float4* ds = xs + 2 * VPT * NT;
+    float* mst = reinterpret_cast<float*>(ds + VPT * NT);  // slot [2k][t] = mu, [2k+1][t] = rstd of this thread's group k
+    float* gsm = mst + 2 * GPT * NT;
+    float* bsm = gsm + g.C;
+    float* redg = bsm + g.C;
+    float4* redc = reinterpret_cast<float4*>(redg + 2 * g.Gt * RG);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int q = t % g.Q, rl = t / g.Q;
+    const int cb = 4 * q;
+    const int M = GPT == 1 ? (g.cpg >> 2) : 1;
+    const int gl = GPT == 1 ? q / M : 2 * q;
+    const bool writer = lane < g.Q && (GPT == 2 || (lane & (M - 1)) == 0);
+    const OStripLanes ln = ostrip_lanes<GPT>(lane, q, g.Q, M);
+    const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
+    const size_t rowoff = (size_t)rl * g.C + cb;
+    const size_t jstride = (size_t)g.RSTEP * g.C;
+    const int G = gridDim.x;
+
+    for (int i = t; i < g.C / 4; i += NT) {
+        reinterpret_cast<float4*>(gsm)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+        if (ACT != ACT_IDENTITY)
+            reinterpret_cast<float4*>(bsm)[i] = __ldg(reinterpret_cast<const float4*>(beta) + i);
+    }
+    int item = blockIdx.x;
+    {   // prologue: x(0) | dy(0) + statistics(0) | x(1)
+        const size_t o0 = dstrip_item_offset(g, item < nitems ? item : 0, rowoff);
+        if (item < nitems) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+                if (FULL || rl + j * g.RSTEP < g.HW)
+                    cp_async16(&xs[j * NT + t], x + o0 + j * jstride);
+        }
+        cp_async_commit();
+        if (item < nitems) {
+            const int gi = (item / g.nct) * g.G + (item % g.nct) * g.Gt + gl;
+#pragma unroll
+            for (int k = 0; k < GPT; ++k) {
+                cp_async4(&mst[(2 * k) * NT + t], mu + gi + k);
+                cp_async4(&mst[(2 * k + 1) * NT + t], rstd + gi + k);
+            }
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+                if (FULL || rl + j * g.RSTEP < g.HW)
+                    cp_async16(&ds[j * NT + t], dy + o0 + j * jstride);
+        }
+        cp_async_commit();
+        if (item + G < nitems) {
+            const size_t o1 = dstrip_item_offset(g, item + G, rowoff);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+                if (FULL || rl + j * g.RSTEP < g.HW)
+                    cp_async16(&xs[(VPT + j) * NT + t], x + o1 + j * jstride);
+        }
+        cp_async_commit();
+    }
+    __syncthreads();  // gamma / beta staged
+
+    int par = 0;
+    for (; item < nitems; item += G, par ^= 1) {
+        const int ctile = item % g.nct, b = item / g.nct;
+        const int c0 = ctile * g.Ct;
+        const size_t base = (size_t)b * g.HW * g.C + c0;
+        const float4 ga = *reinterpret_cast<const float4*>(gsm + c0 + cb);
+        float4 be = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ACT != ACT_IDENTITY)
+            be = *reinterpret_cast<const float4*>(bsm + c0 + cb);
+        const bool more1 = item + G < nitems, more2 = item + 2 * G < nitems;
+        const int it1 = more1 ? item + G : item;
+        const float* n1 = dy + dstrip_item_offset(g, it1, rowoff);
+        const float* n2 = x + dstrip_item_offset(g, more2 ? item + 2 * G : item, rowoff);
+        float4* xc = xs + par * VPT * NT;
+
+        cp_async_wait_but_one();
+        float rsg[GPT], nmg[GPT];
+#pragma unroll
+        for (int k = 0; k < GPT; ++k) {
+            rsg[k] = mst[(2 * k + 1) * NT + t];
+            nmg[k] = -mst[(2 * k) * NT + t] * rsg[k];
+        }
+        if (more1) {
+            const int gi = (it1 / g.nct) * g.G + (it1 % g.nct) * g.Gt + gl;
+#pragma unroll
+            for (int k = 0; k < GPT; ++k) {
+                cp_async4(&mst[(2 * k) * NT + t], mu + gi + k);
+                cp_async4(&mst[(2 * k + 1) * NT + t], rstd + gi + k);
+            }
+        }
+        float4 xv[VPT], dv[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {  // dy slots: read, then re-arm with strip i+1
+            const bool live = FULL || rl + j * g.RSTEP < g.HW;
+            dv[j] = live ? ds[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (more1 && live)
+                cp_async16(&ds[j * NT + t], n1 + j * jstride);
+        }
+        cp_async_commit();
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {  // x slots of this parity: read, then re-arm with strip i+2
+            const bool live = FULL || rl + j * g.RSTEP < g.HW;
+            xv[j] = live ? xc[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (more2 && live)
+                cp_async16(&xc[j * NT + t], n2 + j * jstride);
+        }
+        cp_async_commit();
+
+        // xv becomes xhat, dv becomes dy * act'(z), both kept as packed pairs for the second phase
+        const f32x2 rs01 = pk1(rsg[0]), rs23 = pk1(rsg[GPT - 1]), nm01 = pk1(nmg[0]), nm23 = pk1(nmg[GPT - 1]);
+        const f32x2 ga01 = pk(ga.x, ga.y), ga23 = pk(ga.z, ga.w), be01 = pk(be.x, be.y), be23 = pk(be.z, be.w);
+        f32x2 xa[VPT], xb[VPT], da[VPT], db[VPT];
+        float4 sA, sB;
+        {
+            f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                xa[j] = pk_fma(pk(xv[j].x, xv[j].y), rs01, nm01);
+                xb[j] = pk_fma(pk(xv[j].z, xv[j].w), rs23, nm23);
+                da[j] = pk(dv[j].x, dv[j].y);
+                db[j] = pk(dv[j].z, dv[j].w);
+                if (ACT != ACT_IDENTITY) {
+                    da[j] = pk_mul(da[j], act_slope_x2<ACT>(pk_fma(ga01, xa[j], be01)));
+                    db[j] = pk_mul(db[j], act_slope_x2<ACT>(pk_fma(ga23, xb[j], be23)));
+                }
+                // rows past the end carry dy = 0, so they add nothing to either sum
+                a1 = pk_add(a1, da[j]);
+                b1 = pk_add(b1, db[j]);
+                a2 = pk_fma(da[j], xa[j], a2);
+                b2 = pk_fma(db[j], xb[j], b2);
+            }
+            unpk(a1, sA.x, sA.y);
+            unpk(b1, sA.z, sA.w);
+            unpk(a2, sB.x, sB.y);
+            unpk(b2, sB.z, sB.w);
+        }
+        // per-warp channel sums (all lanes of a float4 column end up with them) ...
+        for (int off = g.Q; off < 32; off <<= 1) {
+            sA = shfl_xor4(sA, off);
+            sB = shfl_xor4(sB, off);
+        }
+        // ... and from them the gamma-weighted per-warp group sums
+        float sg[GPT], sgx[GPT];
+        if constexpr (GPT == 1) {
+            sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y) + fmaf(ga.z, sA.z, ga.w * sA.w);
+            sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y) + fmaf(ga.z, sB.z, ga.w * sB.w);
+            for (int off = 1; off < M; off <<= 1) {
+                sg[0] += __shfl_xor_sync(0xffffffffu, sg[0], off);
+                sgx[0] += __shfl_xor_sync(0xffffffffu, sgx[0], off);
+            }
+        } else {
+            sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y);
+            sg[GPT - 1] = fmaf(ga.z, sA.z, ga.w * sA.w);
+            sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y);
+            sgx[GPT - 1] = fmaf(ga.z, sB.z, ga.w * sB.w);
+        }
+        float* rg = redg + par * g.Gt * RG;
+        float4* rc = redc + (size_t)par * NW * 2 * g.Q;
+        if (lane < g.Q) {
+            rc[(warp * 2 + 0) * g.Q + q] = sA;
+            rc[(warp * 2 + 1) * g.Q + q] = sB;
+            if (writer) {
+#pragma unroll
+                for (int k = 0; k < GPT; ++k)
+                    *reinterpret_cast<float2*>(rg + (gl + k) * RG + 2 * warp) = make_float2(sg[k], sgx[k]);
+            }
+        }
+        __syncthreads();
+
+        float mgv[GPT], mgxv[GPT];
+#pragma unroll
+        for (int k = 0; k < GPT; ++k) {
+            float hi, lo, second;
+            ostrip_group_total<NW, false>(rg + (gl + k) * RG, ln, g.Q, M, hi, lo, second);
+            mgv[k] = hi * inv_n;
+            mgxv[k] = second * inv_n;
+        }
+        // dx = rstd * (g*gamma - mg - xhat*mgx), as in the reference (kernels.cu:692)
+        const f32x2 nmg01 = pk1(-mgv[0]), nmg23 = pk1(-mgv[GPT - 1]), nmx01 = pk1(-mgxv[0]), nmx23 = pk1(-mgxv[GPT - 1]);
+        float* orow = dx + base + rowoff;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (FULL || rl + j * g.RSTEP < g.HW) {
+                float4 o;
+                unpk(pk_mul(rs01, pk_fma(xa[j], nmx01, pk_fma(da[j], ga01, nmg01))), o.x, o.y);
+                unpk(pk_mul(rs23, pk_fma(xb[j], nmx23, pk_fma(db[j], ga23, nmg23))), o.z, o.w);
+                __stcs(reinterpret_cast<float4*>(orow + j * jstride), o);
+            }
+        }
+        if (t < g.Ct) {  // one partial row per sample: [b][0:C] dgamma, [b][C:2C] dbeta
+            const float* rcf = reinterpret_cast<const float*>(rc);
+            float sa = 0.0f, sb = 0.0f;
+#pragma unroll 8
+            for (int w = 0; w < NW; ++w) {
+                sa += rcf[(w * 2 + 0) * g.Ct + t];
+                sb += rcf[(w * 2 + 1) * g.Ct + t];
+            }
+            float* dst = partials + (size_t)b * (2 * g.C) + c0 + t;
+            dst[0] = sb;
+            dst[g.C] = sa;
+        }
+    }
+    cp_async_wait_all();
+}
+
+}  // namespace b200

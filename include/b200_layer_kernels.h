@@ -322,6 +322,10 @@ int b200_device_error_status(void);
 /* Number of kernels this library has launched since load (or since reset). */
 long long b200_launch_count(void);
 void b200_launch_count_reset(void);
+/* Number of GroupNorm launches since load that took kernel family `path`: 0 one strip per CTA, 1 pipelined
+   strips, 2 deep-staged strips, 3 one-barrier strips, 4 chunked strips, 5 generic; -1 for any other value.
+   For tests that must know which family they exercised. */
+long long b200_groupnorm_path_count(int path);
 
 /* Pre-sizes the scratch arena used by the backward kernels on `s` so that no
    allocation happens later (call before capturing a CUDA graph). */

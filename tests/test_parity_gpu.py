@@ -383,6 +383,9 @@ def test_no_bounded_wait_ran_out(lib):
     assert lib.b200_launch_count() > 0
 
 
+_GN_PATH_PIPELINED, _GN_PATH_DEEP, _GN_PATH_ONE_BARRIER = 1, 2, 3
+
+
 @pytest.mark.parametrize("deep,deep_fwd", [(1, 1), (0, 0)])
 @pytest.mark.parametrize("shape", [dict(B=640, HW=1024, C=32, G=4), dict(B=1300, HW=400, C=16, G=2)])
 def test_groupnorm_deep_staged_strips(lib, orc, shape, deep, deep_fwd):
@@ -392,14 +395,53 @@ def test_groupnorm_deep_staged_strips(lib, orc, shape, deep, deep_fwd):
     p = dict(shape, act="silu")
     inp = cases.make_inputs("groupnorm", p, seed=43)
     ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    lib.b200_tune_set(b"gn_one_barrier", 0)  # the one-barrier strips would take these shapes first
     lib.b200_tune_set(b"gn_deep", deep)
     lib.b200_tune_set(b"gn_deep_fwd", deep_fwd)
+    before = lib.b200_groupnorm_path_count(_GN_PATH_DEEP), lib.b200_groupnorm_path_count(_GN_PATH_PIPELINED)
     try:
         got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
         got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
     finally:
+        lib.b200_tune_set(b"gn_one_barrier", 1)
         lib.b200_tune_set(b"gn_deep", 1)
         lib.b200_tune_set(b"gn_deep_fwd", 0)
+    taken = (lib.b200_groupnorm_path_count(_GN_PATH_DEEP) - before[0],
+             lib.b200_groupnorm_path_count(_GN_PATH_PIPELINED) - before[1])
+    assert taken == ((4, 0) if deep else (0, 4)), taken
     _check(got, ref, f"deep={deep}")
     for k in got:
         assert np.array_equal(got[k], got2[k]), k
+
+
+# (B, HW, C, G): channels per group 8, 2, 4, 16, 2 and 8 -- one group per float4 column with 2, 1 and 4
+# columns per group, and two groups per column; rows that fill every register slot (1024, 256) and ragged ones
+_ONE_BARRIER_SHAPES = [dict(B=640, HW=1024, C=32, G=4), dict(B=700, HW=784, C=64, G=32), dict(B=1300, HW=256, C=32, G=8),
+                       dict(B=600, HW=400, C=64, G=4), dict(B=1300, HW=1024, C=16, G=8),
+                       dict(B=320, HW=1024, C=128, G=16)]  # the last one: forward in clusters of 4 CTAs
+
+
+@pytest.mark.parametrize("act", ["silu", None, "mp_silu"])
+@pytest.mark.parametrize("shape", _ONE_BARRIER_SHAPES)
+def test_groupnorm_one_barrier_strips(lib, orc, shape, act):
+    """The one-barrier strips are the default for these shapes (many strips per CTA, whole groups per float4
+    column or two groups per column); checked against the oracle, for bit-reproducibility, and against the
+    three-barrier pipelines on the same inputs."""
+    p = dict(shape, act=act)
+    inp = cases.make_inputs("groupnorm", p, seed=47)
+    ref = cases.oracle_run(orc, "groupnorm", p, inp)
+    before = lib.b200_groupnorm_path_count(_GN_PATH_ONE_BARRIER)
+    got = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    got2 = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    assert lib.b200_groupnorm_path_count(_GN_PATH_ONE_BARRIER) - before == 4, "forward and backward, twice"
+    lib.b200_tune_set(b"gn_one_barrier", 0)
+    try:
+        old = cases.gpu_run(lib, "groupnorm", p, inp, fused=True)
+    finally:
+        lib.b200_tune_set(b"gn_one_barrier", 1)
+    assert lib.b200_groupnorm_path_count(_GN_PATH_ONE_BARRIER) - before == 4
+    _check(got, ref, f"one barrier {shape} {act}")
+    for k in got:
+        assert np.array_equal(got[k], got2[k]), k
+        tol = cases.TOL_FWD if k in ("y", "mu", "rstd") else cases.TOL_BWD
+        assert cases.rel_err(got[k], old[k]) <= tol, (k, cases.rel_err(got[k], old[k]))
