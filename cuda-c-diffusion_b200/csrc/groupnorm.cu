@@ -212,6 +212,9 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
                 vpt *= 2;
             if (vpt > max_vpt)
                 continue;
+            // backward (two tensors per thread): 8 rows per tensor only fit 512-thread CTAs
+            if (ctas_per_sm_hint == 1 && vpt == 8 && NT != 512)
+                continue;
             long score = 0;
             if (Ct * 4 >= 64)
                 score += 1000000;
@@ -433,6 +436,100 @@ static bool strip_too_narrow(const StripPlan& plan, int HW, int C, int G)
     return cstrip_plan(&wide, HW, C, G) && wide.g.Ct > plan.g.Ct;
 }
 
+// Exact-fill plans for the one-barrier kernels: CTAs of 7 * 64 or 7 * 128 threads whose 7 register slots per thread
+// hold exactly HW rows (HW = 7 * NT / Q; 28 x 28 and 14 x 14 samples), so that the predicate-free FULL kernels apply
+// where the power-of-two CTAs would leave a quarter of their slots empty.
+static bool exact7_plan(StripPlan* out, int HW, int C, int G, int NT)
+{
+    if (C % 4 != 0 || C % G != 0 || HW % 7 != 0)
+        return false;
+    const int cpg = C / G;
+    for (int Q = 32; Q >= 1; Q >>= 1) {  // widest strip first
+        const int Ct = 4 * Q;
+        if (NT % Q != 0 || (NT / Q) * 7 != HW || C % Ct != 0 || Ct % cpg != 0 || Ct * 4 < 64)
+            continue;
+        StripGeom g;
+        g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = NT / Q;
+        g.Gt = Ct / cpg; g.nct = C / Ct;
+        g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+        out->NT = NT;
+        out->VPT = 7;
+        out->g = g;
+        out->smem = 0;
+        return ostrip_gpt(g) != 0;
+    }
+    return false;
+}
+
+template <int ACT>
+static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, const float* gamma, const float* beta,
+    int B, int HW, int C, int G, float eps, cudaStream_t s)
+{
+    if (!tune_get("gn_exact7", 1) || !tune_get("gn_one_barrier", 1))
+        return false;
+    // one 896-thread CTA per SM (wider strips) when that leaves every CTA at least 6 strips, else two of 448 threads
+    StripPlan plan;
+    int per_sm = 1;
+    long grid = 0, resident = 0, per_cta = 0;
+    const int forced = tune_get("gn_exact7_fwd_nt", 0);
+    for (int pass = 0; pass < 2; ++pass) {
+        const int NT = pass == 0 ? 896 : 448;
+        per_cta = 0;
+        if ((forced && forced != NT) || !exact7_plan(&plan, HW, C, G, NT))
+            continue;
+        per_sm = NT == 896 ? 1 : 2;
+        grid = (long)B * plan.g.nct;
+        resident = (long)sm_count() * per_sm;
+        if (grid <= resident || grid > 2147483647L)
+            continue;
+        per_cta = (grid + resident - 1) / resident;
+        if (per_cta >= (NT == 896 ? 6 : tune_get("gn_exact7_min_fwd", 2)))
+            break;
+        per_cta = 0;
+    }
+    if (per_cta == 0)
+        return false;
+    const long pgrid = (grid + per_cta - 1) / per_cta;
+    const int gpt = ostrip_gpt(plan.g);
+    const size_t osmem = (size_t)plan.VPT * plan.NT * 16
+        + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * (plan.NT / 32) + 4)) * sizeof(float);
+    if (osmem * per_sm > 226 * 1024)
+        return false;
+    const bool full = true;
+    OSTRIP_FWD_CASE(896, 7, 1) OSTRIP_FWD_CASE(448, 7, 2)
+    return false;
+}
+
+template <int ACT>
+static bool gn_backward_exact7(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+    const float* gamma, const float* beta, const float* mu, const float* rstd, int B, int HW, int C, int G,
+    cudaStream_t s)
+{
+    if (!tune_get("gn_exact7", 1) || !tune_get("gn_one_barrier", 1))
+        return false;
+    StripPlan plan;
+    if (!exact7_plan(&plan, HW, C, G, 448))
+        return false;
+    const long grid = (long)B * plan.g.nct, resident = sm_count();
+    if (grid <= resident || grid > 2147483647L)
+        return false;
+    const long per_cta = (grid + resident - 1) / resident;
+    const long pgrid = (grid + per_cta - 1) / per_cta;
+    if (per_cta < tune_get("gn_exact7_min_bwd", 6))
+        return false;
+    const int gpt = ostrip_gpt(plan.g), nw = plan.NT / 32;
+    const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
+        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * nw + 4)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16;
+    if (osmem > 226 * 1024)
+        return false;
+    Scratch sc;
+    if (!scratch_get(s, (size_t)2 * B * C, 0, &sc))
+        return false;
+    const bool full = true;
+    OSTRIP_BWD_CASE(448, 7)
+    return false;
+}
+
 template <int ACT>
 static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, const float* gamma,
     const float* beta, int B, int HW, int C, int G, float eps, cudaStream_t s)
@@ -444,6 +541,8 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
             return false;
         if (!(aligned16(y) && aligned16(x) && aligned16(gamma) && aligned16(beta)) || (long)B * HW * C >= 2147483648L)
             return false;
+        if (gn_forward_exact7<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
+            return true;
         StripPlan plan;
         if (!strip_plan(&plan, B, HW, C, G, 8, tune_get("gn_fwd_strip_ct", 0), tune_get("gn_fwd_strip_nt", 0), 0))
             return false;
@@ -473,7 +572,8 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 if (gpt && osmem * per_sm <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min_fwd", 3)) {
                     // clusters of 4 neighbouring strips, staged in step (see gn_fwd_ostrip)
                     const int cw = tune_get("gn_fwd_cluster", 4);
-                    const bool clustered = cw > 1 && per_sm == 1 && full && plan.g.nct % cw == 0 && per_cta >= 8;
+                    const bool clustered = cw > 1 && per_sm == 1 && (full || tune_get("gn_fwd_cluster_ragged", 0)) && plan.g.nct % cw == 0
+                        && per_cta >= tune_get("gn_fwd_cluster_min", 8);
                     ClusterScope cluster(clustered ? cw : 1);
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
@@ -508,6 +608,8 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
             return false;
         if (ACT != ACT_IDENTITY && !aligned16(beta))
             return false;
+        if (gn_backward_exact7<ACT>(dx, dgamma, dbeta, dy, x, gamma, beta, mu, rstd, B, HW, C, G, s))
+            return true;
         StripPlan plan;
         const int force_nt = tune_get("gn_bwd_strip_nt", 0);
         // 512-thread CTAs may hold 8 rows per tensor (one CTA per SM, 128 registers per thread)
@@ -543,7 +645,7 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                     + (size_t)2 * nw * 2 * plan.g.Q * 16;
                 // (a cluster barrier per strip, as in the forward kernel, was measured here too: 0.89 -> 0.78 with
                 // pairs, worse with wider clusters -- the backward has no idle time to absorb the lock step)
-                if (gpt && per_sm == 1 && osmem <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min", 8)) {
+                if (gpt && per_sm == 1 && osmem <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min", 6)) {
                     OSTRIP_BWD_CASE(1024, 4) OSTRIP_BWD_CASE(512, 4) OSTRIP_BWD_CASE(512, 8)
                 }
                 if (tune_get("gn_deep", 1) && per_sm == 1 && dsmem <= 226 * 1024 && grid >= 8 * pgrid) {
