@@ -32,6 +32,7 @@
 #include "../../include/b200_layer_kernels.h"
 
 #include <atomic>
+#include <mutex>
 
 namespace b200 {
 
@@ -284,10 +285,31 @@ static bool strip_launch(int path, void (*kernel)(KArgs...), long grid, int NT, 
         cfg.attrs = at;
         cfg.numAttrs = nat;
         cfg.gridDim.x = (unsigned)((grid + w - 1) / w * w);
-        int nclusters = 0;
-        if (cfg.gridDim.x == 0 || cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess || nclusters < 1) {
-            (void)cudaGetLastError();
-            return false;
+        // resident clusters of this kernel at this size: asked of the driver once per (kernel, device, size)
+        struct Known {
+            const void* fn;
+            int dev, w, nt, clusters;
+            size_t smem;
+        };
+        static Known known[32];
+        static int nknown = 0;
+        static std::mutex mu;
+        int dev = 0, nclusters = 0;
+        (void)cudaGetDevice(&dev);
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            for (int i = 0; i < nknown; ++i)
+                if (known[i].fn == (const void*)kernel && known[i].dev == dev && known[i].w == w && known[i].nt == NT
+                    && known[i].smem == smem)
+                    nclusters = known[i].clusters;
+            if (nclusters == 0) {
+                if (cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess || nclusters < 1) {
+                    (void)cudaGetLastError();
+                    return false;
+                }
+                if (nknown < 32)
+                    known[nknown++] = Known{ (const void*)kernel, dev, w, NT, nclusters, smem };
+            }
         }
         if ((long)nclusters * w < (long)cfg.gridDim.x)
             cfg.gridDim.x = (unsigned)(nclusters * w);

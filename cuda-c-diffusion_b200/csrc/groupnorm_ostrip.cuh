@@ -161,10 +161,13 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 #pragma unroll
         for (int k = 0; k < GPT; ++k)
             cp_async4(&kst[k * NT + t], x + sb + koff + k * g.cpg);
+        const float* src = x + sb + rowoff;  // advanced row block by row block: one 64-bit add per copy
 #pragma unroll
-        for (int j = 0; j < VPT; ++j)
+        for (int j = 0; j < VPT; ++j) {
             if (FULL || rl + j * g.RSTEP < g.HW)
-                cp_async16(&stage[j * NT + t], x + sb + rowoff + j * jstride);
+                cp_async16(&stage[j * NT + t], src);
+            src += jstride;
+        }
     };
     int item = blockIdx.x;
     if (item < nitems)
@@ -285,8 +288,9 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
                 float4 o;
                 unpk(act_value_x2<ACT>(pk_fma(pk(v[j].x, v[j].y), sc01, sh01)), o.x, o.y);
                 unpk(act_value_x2<ACT>(pk_fma(pk(v[j].z, v[j].w), sc23, sh23)), o.z, o.w);
-                __stcs(reinterpret_cast<float4*>(yrow + j * jstride), o);
+                __stcs(reinterpret_cast<float4*>(yrow), o);
             }
+            yrow += jstride;
         }
     }
     cp_async_wait_all();
@@ -396,20 +400,24 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             }
         }
         float4 xv[VPT], dv[VPT];
+        const float* s1 = n1;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {  // dy slots: read, then re-arm with strip i+1
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
             dv[j] = live ? ds[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (more1 && live)
-                cp_async16(&ds[j * NT + t], n1 + j * jstride);
+                cp_async16(&ds[j * NT + t], s1);
+            s1 += jstride;
         }
         cp_async_commit();
+        const float* s2 = n2;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {  // x slots of this parity: read, then re-arm with strip i+2
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
             xv[j] = live ? xc[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (more2 && live)
-                cp_async16(&xc[j * NT + t], n2 + j * jstride);
+                cp_async16(&xc[j * NT + t], s2);
+            s2 += jstride;
         }
         cp_async_commit();
 
@@ -491,8 +499,9 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 float4 o;
                 unpk(pk_mul(rs01, pk_fma(xa[j], nmx01, pk_fma(da[j], ga01, nmg01))), o.x, o.y);
                 unpk(pk_mul(rs23, pk_fma(xb[j], nmx23, pk_fma(db[j], ga23, nmg23))), o.z, o.w);
-                __stcs(reinterpret_cast<float4*>(orow + j * jstride), o);
+                __stcs(reinterpret_cast<float4*>(orow), o);
             }
+            orow += jstride;
         }
         if (t < g.Ct) {  // one partial row per sample: [b][0:C] dgamma, [b][C:2C] dbeta
             const float* rcf = reinterpret_cast<const float*>(rc);
