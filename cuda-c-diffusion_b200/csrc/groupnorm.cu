@@ -518,6 +518,7 @@ static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, 
     if (osmem * per_sm > 226 * 1024)
         return false;
     const bool full = true;
+    plan.g.stagger_lo = per_cta >= 8;  // paced stores in the kernels without activation
     OSTRIP_FWD_CASE(896, 7, 1) OSTRIP_FWD_CASE(448, 7, 2)
     return false;
 }
@@ -597,6 +598,7 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                     const bool clustered = cw > 1 && per_sm == 1 && (full || tune_get("gn_fwd_cluster_ragged", 0)) && plan.g.nct % cw == 0
                         && per_cta >= tune_get("gn_fwd_cluster_min", 8);
                     ClusterScope cluster(clustered ? cw : 1);
+                    plan.g.stagger_lo = per_cta >= 8;  // paced stores in the kernels without activation
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
                 }

@@ -43,6 +43,30 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
 }
 
+// 128-bit shared-memory load that stays ONE instruction (left to the compiler, the backward's staging reads
+// came out as four 32-bit loads each: 74 instead of 23 shared loads per thread and strip)
+__device__ __forceinline__ float4 lds128(const float4* p)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_addr(p)) : "memory");
+    return v;
+}
+
+// cp.async.wait_group with a run-time count in 0..7 (folds to one instruction where the count is known after unrolling)
+__device__ __forceinline__ void cp_async_wait_pending(int n)
+{
+    switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
+}
+
 // Lanes of a warp that share a group: Lg of them, this lane being number li (the same numbering in every
 // warp, so every warp derives bit-identical totals from the same partials).
 struct OStripLanes {
@@ -150,6 +174,13 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
     const size_t rowoff = (size_t)rl * g.C + cb;
     const size_t jstride = (size_t)g.RSTEP * g.C;
     const int G = gridDim.x;
+    // Without an activation the second phase is a few instructions per element, and 128 KB of stores would leave
+    // in one burst; measured, stores spread over the strip period serve DRAM better (0.84 -> 0.89 of the copy rate on
+    // [256,32,32,256]; a fixed 250 ns between row blocks: 0.91).  So there each row block's store waits until one
+    // more row block of the NEXT strip has landed: stores leave at the rate at which loads arrive.  With SiLU the
+    // arithmetic already paces the stores and the same scheme costs 5 %.
+    // Only for launches with many strips per CTA (the host sets g.stagger_lo): with 2-4 strips the waits cost more.
+    const bool paced = ACT == ACT_IDENTITY && VPT <= 8 && g.stagger_lo != 0;
 
     for (int i = t; i < g.C / 4; i += NT) {
         reinterpret_cast<float4*>(gsm)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);
@@ -167,6 +198,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
             if (FULL || rl + j * g.RSTEP < g.HW)
                 cp_async16(&stage[j * NT + t], src);
             src += jstride;
+            if (paced && j + 1 < VPT)
+                cp_async_commit();  // one group per slot (the caller commits the last)
         }
     };
     int item = blockIdx.x;
@@ -201,6 +234,11 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
             asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
         if (item + G < nitems)
             stage_item(item + G);
+        else if (paced) {
+#pragma unroll
+            for (int j = 0; j + 1 < VPT; ++j)
+                cp_async_commit();  // empty groups keep the count per strip the same
+        }
         cp_async_commit();
 
         float S1[GPT], S2[GPT];
@@ -291,6 +329,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
                 __stcs(reinterpret_cast<float4*>(yrow), o);
             }
             yrow += jstride;
+            if (paced)
+                cp_async_wait_pending(VPT - 1 - j);
         }
     }
     cp_async_wait_all();
@@ -404,7 +444,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {  // dy slots: read, then re-arm with strip i+1
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            dv[j] = live ? ds[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            dv[j] = live ? lds128(&ds[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (more1 && live)
                 cp_async16(&ds[j * NT + t], s1);
             s1 += jstride;
@@ -414,7 +454,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {  // x slots of this parity: read, then re-arm with strip i+2
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            xv[j] = live ? xc[j * NT + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[j] = live ? lds128(&xc[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (more2 && live)
                 cp_async16(&xc[j * NT + t], s2);
             s2 += jstride;
