@@ -641,10 +641,10 @@ def ddpm_dp_train(world, rank, local_rank, batch_per_gpu, steps=30, warmup=5, sh
 KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd": 2 * NEL * 4, "ln_bwd": 3 * NEL * 4,
                 "sinusoidal": B * EMB * 4}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-# (captured at batch 128 and scaled by 2 to the full launch; traffic grows linearly with the batch).  Reads
-# match the algorithmic bytes; the write figure is low because up to an L2's worth of dirty lines has
-# not been written back when the kernel ends.
-NCU_TRAFFIC = {"gn_silu_bwd": 2 * (268_502_016 + 92_896_256), "gn_silu_fwd": 2 * (134_456_576 + 79_868_672),
+# (GroupNorm: captured at the full batch; LayerNorm: at batch 128 and scaled by 2, traffic grows linearly with the
+# batch).  Reads match the algorithmic bytes; the write figure is low because up to an L2's worth of dirty lines
+# has not been written back when the kernel ends.
+NCU_TRAFFIC = {"gn_silu_bwd": 536_966_400 + 226_842_880, "gn_silu_fwd": 268_462_336 + 210_558_976,
                "ln_fwd": 2 * (134_267_904 + 83_640_064), "ln_bwd": 2 * (269_501_952 + 95_807_232)}
 
 
