@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 cp_async4(&mst[(2 * k + 1) * NT + t], rstd + gi + k);
             }
         }
-        float4 xv[VPT], dv[VPT];
+        float4 dv[VPT];
         const float* s1 = n1;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {  // dy slots: read, then re-arm with strip i+1
@@ -450,28 +450,25 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             s1 += jstride;
         }
         cp_async_commit();
-        const float* s2 = n2;
-#pragma unroll
-        for (int j = 0; j < VPT; ++j) {  // x slots of this parity: read, then re-arm with strip i+2
-            const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            xv[j] = live ? lds128(&xc[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (more2 && live)
-                cp_async16(&xc[j * NT + t], s2);
-            s2 += jstride;
-        }
-        cp_async_commit();
-
-        // xv becomes xhat, dv becomes dy * act'(z), both kept as packed pairs for the second phase
+        // xv becomes xhat, dv becomes dy * act'(z), both kept as packed pairs for the second phase.  The x slots of
+        // this parity are read one row block at a time, each re-armed with strip i+2 right behind its read and
+        // followed by its arithmetic, so that shared-memory traffic and arithmetic overlap within the warp.
         const f32x2 rs01 = pk1(rsg[0]), rs23 = pk1(rsg[GPT - 1]), nm01 = pk1(nmg[0]), nm23 = pk1(nmg[GPT - 1]);
         const f32x2 ga01 = pk(ga.x, ga.y), ga23 = pk(ga.z, ga.w), be01 = pk(be.x, be.y), be23 = pk(be.z, be.w);
         f32x2 xa[VPT], xb[VPT], da[VPT], db[VPT];
         float4 sA, sB;
         {
             f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
+            const float* s2 = n2;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                xa[j] = pk_fma(pk(xv[j].x, xv[j].y), rs01, nm01);
-                xb[j] = pk_fma(pk(xv[j].z, xv[j].w), rs23, nm23);
+                const bool live = FULL || rl + j * g.RSTEP < g.HW;
+                const float4 xv = live ? lds128(&xc[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (more2 && live)
+                    cp_async16(&xc[j * NT + t], s2);
+                s2 += jstride;
+                xa[j] = pk_fma(pk(xv.x, xv.y), rs01, nm01);
+                xb[j] = pk_fma(pk(xv.z, xv.w), rs23, nm23);
                 da[j] = pk(dv[j].x, dv[j].y);
                 db[j] = pk(dv[j].z, dv[j].w);
                 if (ACT != ACT_IDENTITY) {
@@ -484,6 +481,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 a2 = pk_fma(da[j], xa[j], a2);
                 b2 = pk_fma(db[j], xb[j], b2);
             }
+            cp_async_commit();
             unpk(a1, sA.x, sA.y);
             unpk(b1, sA.z, sA.w);
             unpk(a2, sB.x, sB.y);
