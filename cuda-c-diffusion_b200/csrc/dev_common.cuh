@@ -89,17 +89,24 @@ int* device_error_word();
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Every kernel of the library is launched through launch_k.  With programmatic dependent launch on
-// (tunable "pdl", default 1) a kernel may be scheduled while the kernel before it on the stream is
-// still draining: its CTAs take the SMs that fall free during the predecessor's last wave and stop at
-// pdl_prologue() until the predecessor has completed and its writes are visible.  That removes the
-// launch gap (1.5-3 us) between back-to-back kernels of this library, which is most of the run time
-// of the small layers of a training step.  A predecessor that is not one of these kernels (cuBLAS, a
-// copy) simply completes first, as in an ordinary launch; inside stream capture the dependency
-// becomes a programmatic edge of the graph.
-inline void pdl_attribute(cudaLaunchAttribute* at, unsigned* n)
+// Every kernel of the library is launched through launch_k.  With programmatic dependent launch (tunable
+// "pdl": 1 = small launches only, the default; 2 = every launch; 0 = never) a kernel may be scheduled
+// while the kernel before it on the stream is still draining: its CTAs take the SMs that fall free during
+// the predecessor's last wave and stop at pdl_prologue() until the predecessor has completed and its
+// writes are visible.  That removes the launch gap (1.5-3 us) between back-to-back kernels of this
+// library, which is most of the run time of the small layers of a training step.  A predecessor that is
+// not one of these kernels (cuBLAS, a copy) simply completes first, as in an ordinary launch; inside
+// stream capture the dependency becomes a programmatic edge of the graph.
+// Large launches are excluded because there it costs: back to back, the four big kernels of the
+// benchmark step ([256,32,32,256]) take 0.485-0.490 ms with the attribute and 0.456-0.460 ms without.
+// CTAs of a dependent grid are placed on SMs in the order in which the predecessor frees them rather
+// than all at once, and the bandwidth these kernels reach depends on which CTAs run side by side.
+// `threads` = CTAs x threads per CTA of the launch.
+constexpr long PDL_MAX_THREADS = 98304;  // a third of the 148 x 2048 resident threads
+inline void pdl_attribute(cudaLaunchAttribute* at, unsigned* n, long threads)
 {
-    if (tune_get("pdl", 1)) {
+    const int mode = tune_get("pdl", 1);
+    if (mode == 2 || (mode == 1 && threads <= PDL_MAX_THREADS)) {
         at[*n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[*n].val.programmaticStreamSerializationAllowed = 1;
         ++*n;
@@ -116,7 +123,7 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
     cfg.stream = s;
     cudaLaunchAttribute at[1];
     unsigned n = 0;
-    pdl_attribute(at, &n);
+    pdl_attribute(at, &n, (long)grid.x * grid.y * grid.z * block.x * block.y * block.z);
     cfg.attrs = at;
     cfg.numAttrs = n;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in B200_CHECK_LAUNCH

@@ -274,7 +274,7 @@ static bool strip_launch(int path, void (*kernel)(KArgs...), long grid, int NT, 
     cfg.stream = s;
     cudaLaunchAttribute at[2];
     unsigned nat = 0;
-    pdl_attribute(at, &nat);
+    pdl_attribute(at, &nat, grid * NT);
     if (t_gn_cluster > 1) {
         const int w = t_gn_cluster;
         at[nat].id = cudaLaunchAttributeClusterDimension;

@@ -292,7 +292,7 @@ static void wn_launch_cluster_fwd(const WnTable& tb, int cs, float eps, cudaStre
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     unsigned nat = 1;
-    pdl_attribute(attr, &nat);
+    pdl_attribute(attr, &nat, (long)cs * tb.strip0[tb.count] * WN_THREADS);
     cfg.attrs = attr;
     cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, wn_forward_cluster, tb, eps);
@@ -316,7 +316,7 @@ static void wn_launch_cluster_bwd(const WnGradTable& tb, int cs, cudaStream_t s)
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     unsigned nat = 1;
-    pdl_attribute(attr, &nat);
+    pdl_attribute(attr, &nat, (long)cs * tb.strip0[tb.count] * WN_THREADS);
     cfg.attrs = attr;
     cfg.numAttrs = nat;
     cudaError_t e = cudaLaunchKernelEx(&cfg, wn_backward_cluster, tb);
