@@ -99,8 +99,9 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // stream capture the dependency becomes a programmatic edge of the graph.
 // Large launches are excluded because there it costs: back to back, the four big kernels of the
 // benchmark step ([256,32,32,256]) take 0.485-0.490 ms with the attribute and 0.456-0.460 ms without.
-// CTAs of a dependent grid are placed on SMs in the order in which the predecessor frees them rather
-// than all at once, and the bandwidth these kernels reach depends on which CTAs run side by side.
+// (The likely cause: CTAs of a dependent grid are placed on SMs in the order in which the predecessor
+// frees them rather than all at once, and the bandwidth the strided kernels reach depends on which CTAs
+// run side by side -- see groupnorm_ostrip.cuh.)
 // `threads` = CTAs x threads per CTA of the launch.
 constexpr long PDL_MAX_THREADS = 98304;  // a third of the 148 x 2048 resident threads
 inline void pdl_attribute(cudaLaunchAttribute* at, unsigned* n, long threads)
