@@ -443,6 +443,29 @@ def ops_table(lib, fused, peak, only=None):
     add("cfg1_weight_norm_fwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize(P(Wm), 1152, 128, F(1e-4), st()), 1, 100), 2 * Wm.numel() * 4)
     add("cfg1_weight_norm_bwd_1152x128", graph_time(lib, lambda i: lib.launch_weight_normalize_backward(P(Mm), P(Wm), P(gain), P(gg), 1152, 128, st()), 1, 100), 3 * Wm.numel() * 4)
 
+    # ---- config 2: the two GroupNorm+SiLU kernels of the step and LayerNorm, each ALONE (the step's per-kernel
+    # times also carry the write-backs of whatever ran before)
+    b2, hw2, c2, g2 = 256, 1024, 256, 32
+    n2 = b2 * hw2 * c2
+    X2 = [torch.randn(b2, hw2, c2, device=dev) for _ in range(2)]
+    D2 = [torch.randn(b2, hw2, c2, device=dev) for _ in range(2)]
+    Y2 = [torch.empty(b2, hw2, c2, device=dev) for _ in range(2)]
+    gam2, bet2 = 1 + 0.1 * torch.randn(c2, device=dev), 0.1 * torch.randn(c2, device=dev)
+    mu2, rs2 = torch.empty(b2 * hw2, device=dev), torch.empty(b2 * hw2, device=dev)
+    dg2, db2 = torch.empty(c2, device=dev), torch.empty(c2, device=dev)
+    if fused:
+        add("cfg2_groupnorm_silu_fwd_alone", graph_time(lib, lambda i: lib.launch_groupnorm_act_forward(
+            P(Y2[i]), P(mu2), P(rs2), P(X2[i]), P(gam2), P(bet2), b2, hw2, c2, g2, F(1e-5), 3, st()), 2, 40), 2 * n2 * 4)
+        add("cfg2_groupnorm_silu_bwd_alone", graph_time(lib, lambda i: lib.launch_groupnorm_act_backward(
+            P(Y2[i]), P(dg2), P(db2), P(D2[i]), P(X2[i]), P(gam2), P(bet2), P(mu2), P(rs2), b2, hw2, c2, g2, 3, st()),
+            2, 40, 2 * b2 * c2 * 4), 3 * n2 * 4)
+    add("cfg2_layernorm_fwd_alone", graph_time(lib, lambda i: lib.launch_layernorm_forward(
+        P(Y2[i]), P(mu2), P(rs2), P(X2[i]), P(gam2), P(bet2), b2 * hw2, c2, F(1e-5), st()), 2, 40 if fused else 4), 2 * n2 * 4)
+    add("cfg2_layernorm_bwd_alone", graph_time(lib, lambda i: lib.launch_layernorm_backward(
+        P(Y2[i]), P(dg2), P(db2), P(D2[i]), P(X2[i]), P(gam2), P(mu2), P(rs2), b2 * hw2, c2, st()), 2, 40 if fused else 4,
+        64 << 20), 3 * n2 * 4)
+    del X2, D2, Y2
+
     # ---- embeddings (latency-bound)
     tt = torch.randint(0, 1000, (256,), device=dev).float(); e1 = torch.empty(256, 512, device=dev)
     add("cfg2_sinusoidal_256x512", graph_time(lib, lambda i: lib.launch_sinusoidal(P(e1), P(tt), 256, 512, F(9.2103404), st()), 1, 100), e1.numel() * 4)
