@@ -538,8 +538,19 @@ static bool gn_backward_exact7(float* dx, float* dgamma, float* dbeta, const flo
         return false;
     const long per_cta = (grid + resident - 1) / resident;
     const long pgrid = (grid + per_cta - 1) / per_cta;
-    if (per_cta < tune_get("gn_exact7_min_bwd", 6))
+    if (per_cta < tune_get("gn_exact7_min_bwd", 6)) {
+        // few strips per CTA: the three-barrier pipeline on the same exact-fill geometry, where there is an activation
+        // to pay for ([128,28,28,64]: 21.9 -> 20.4 us with SiLU, but 18.0 -> 18.6 us without)
+        if (ACT == ACT_IDENTITY || !tune_get("gn_exact7_pstrip", 1))
+            return false;
+        const int red = 2 * (plan.NT / 32) * plan.g.Ct;
+        const size_t psmem = (size_t)2 * plan.VPT * plan.NT * 16 + (size_t)(red + 2 * plan.g.Ct + 2 * plan.g.Gt) * sizeof(float);
+        Scratch sc;
+        if (psmem > 220 * 1024 || !scratch_get(s, (size_t)2 * B * C, 0, &sc))
+            return false;
+        PSTRIP_BWD_CASE(448, 7, 1)
         return false;
+    }
     const int gpt = ostrip_gpt(plan.g), nw = plan.NT / 32;
     const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
         + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * nw + 4)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16;
