@@ -54,6 +54,13 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
     const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
     const int R = g.RSTEP * VPT;  // rows per chunk
 
+    // In a cluster launch (see gn_fwd_ostrip) the CTAs of a cluster walk neighbouring column tiles of the same rows
+    // and keep their staging bursts in step with a cluster barrier per chunk; every CTA of a cluster runs the same
+    // number of chunks (grid and item count multiples of the cluster width), else nobody touches the barrier.
+    unsigned csize;
+    asm("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
+    const bool csync = csize > 1 && (int)gridDim.x % (int)csize == 0 && nitems % (int)csize == 0;
+
     int item = blockIdx.x;
     int ctile = item % g.nct, b = item / g.nct;
     const int step_ct = (int)gridDim.x % g.nct, step_b = (int)gridDim.x / g.nct;
@@ -74,6 +81,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
         // ---- pass 1: shifted sums over all chunks
         for (int k = 0; k < nchunks; ++k) {
             cp_async_wait_all();
+            if (csync)
+                asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
             float4 v[VPT];
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
@@ -81,6 +90,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
                 if (k * R + rl + j * g.RSTEP >= g.HW)
                     v[j] = K;  // rows past the end contribute zero
             }
+            if (csync)
+                asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
             // next: the following chunk, or chunk 0 again for the second pass
             cstrip_prefetch<NT, VPT, 1>(stage, g, base, (k + 1 < nchunks) ? (k + 1) * R : 0, rl, x, nullptr);
 #pragma unroll
@@ -130,10 +141,14 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
         // ---- pass 2: normalise, activate, store
         for (int k = 0; k < nchunks; ++k) {
             cp_async_wait_all();
+            if (csync)
+                asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
             float4 v[VPT];
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 v[j] = stage[j * NT + t];
+            if (csync)
+                asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
             if (k + 1 < nchunks)
                 cstrip_prefetch<NT, VPT, 1>(stage, g, base, (k + 1) * R, rl, x, nullptr);
             else if (item + (int)gridDim.x < nitems)
