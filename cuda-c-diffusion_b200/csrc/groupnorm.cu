@@ -750,8 +750,6 @@ static bool gn_forward_cstrip(float* y, float* mu, float* rstd, const float* x, 
         const int nchunks = (HW + plan.g.RSTEP * VPT - 1) / (plan.g.RSTEP * VPT);
         const size_t psmem = (size_t)VPT * plan.NT * 16 + plan.smem;
         static bool done4[64] = { false }, done8[64] = { false };
-        const int cw = tune_get("gn_cstrip_cluster", 1);
-        ClusterScope cluster(cw > 1 && plan.g.nct % cw == 0 ? cw : 1);
         if (VPT == 8)
             return pstrip_launch(GN_PATH_CHUNKED, gn_fwd_cstrip<512, 8, ACT, MB>, done8, pgrid, 512, psmem, s, y, mu, rstd, x, gamma, beta,
                 plan.g, eps, (int)items, nchunks);

@@ -14,7 +14,10 @@
 // byte once; beyond that the strip is read from DRAM twice, which is still fewer bytes and far
 // fewer barriers than the tile kernels need.
 // (A two-deep ring of chunk buffers over a flattened (strip, pass, chunk) sequence was measured:
-// 10 % faster on 128x128 samples, 8-12 % slower on 64x64 ones with an activation; not kept.)
+// 10 % faster on 128x128 samples, 8-12 % slower on 64x64 ones with an activation; not kept.
+// So was the cluster barrier in front of every staging burst that helps the register-resident forward
+// (groupnorm_ostrip.cuh): here, with two barriers per chunk, [32,64,64,256] went from 0.67 to 0.57-0.59
+// of the copy rate and [16,128,128,128] from 0.51 to 0.37-0.42.)
 #pragma once
 
 namespace b200 {
@@ -54,13 +57,6 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
     const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
     const int R = g.RSTEP * VPT;  // rows per chunk
 
-    // In a cluster launch (see gn_fwd_ostrip) the CTAs of a cluster walk neighbouring column tiles of the same rows
-    // and keep their staging bursts in step with a cluster barrier per chunk; every CTA of a cluster runs the same
-    // number of chunks (grid and item count multiples of the cluster width), else nobody touches the barrier.
-    unsigned csize;
-    asm("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
-    const bool csync = csize > 1 && (int)gridDim.x % (int)csize == 0 && nitems % (int)csize == 0;
-
     int item = blockIdx.x;
     int ctile = item % g.nct, b = item / g.nct;
     const int step_ct = (int)gridDim.x % g.nct, step_b = (int)gridDim.x / g.nct;
@@ -81,8 +77,6 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
         // ---- pass 1: shifted sums over all chunks
         for (int k = 0; k < nchunks; ++k) {
             cp_async_wait_all();
-            if (csync)
-                asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
             float4 v[VPT];
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
@@ -90,8 +84,6 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
                 if (k * R + rl + j * g.RSTEP >= g.HW)
                     v[j] = K;  // rows past the end contribute zero
             }
-            if (csync)
-                asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
             // next: the following chunk, or chunk 0 again for the second pass
             cstrip_prefetch<NT, VPT, 1>(stage, g, base, (k + 1 < nchunks) ? (k + 1) * R : 0, rl, x, nullptr);
 #pragma unroll
@@ -141,14 +133,10 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_cstrip(float* __restrict__ y, f
         // ---- pass 2: normalise, activate, store
         for (int k = 0; k < nchunks; ++k) {
             cp_async_wait_all();
-            if (csync)
-                asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
             float4 v[VPT];
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 v[j] = stage[j * NT + t];
-            if (csync)
-                asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
             if (k + 1 < nchunks)
                 cstrip_prefetch<NT, VPT, 1>(stage, g, base, (k + 1) * R, rl, x, nullptr);
             else if (item + (int)gridDim.x < nitems)
