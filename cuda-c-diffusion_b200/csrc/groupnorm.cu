@@ -23,7 +23,12 @@
 // half of the second pass's reads hit L2.  And for small launches, where a strip's latency chain rather
 // than bandwidth sets the time, the rows of a strip split over a cluster of 2 or 4 CTAs with one DSMEM
 // exchange of the partial sums: [128,28,28,64] took 15.7-37 us forward and 28-41 us backward against
-// 12.2 / 18.0 us for the plain strips -- two cluster barriers cost more than half a strip's latency.
+// 12.2 / 18.0 us for the plain strips -- two cluster barriers cost more than half a strip's latency.  The
+// same split for samples too tall for one CTA (one-barrier kernels, every warp pushing its group sums into
+// the shared memory of all CTAs of the cluster, ONE cluster barrier per strip, x read once): [32,64,64,256]
+// 76 us forward / 101-120 us backward against 62 / 102 us for the chunked strips, which read x twice but the
+// second time from L2 -- the barrier between the two phases waits for the slowest of 4-8 CTAs with nothing
+// else resident on the SM (with remote LOADS after the barrier instead of remote stores before it: 131 us).
 //
 // Backward in every family reuses the per-channel sums of g and g*xhat (g = dy * act'(z)) for BOTH
 // the group sums that dx needs and the per-sample dgamma/dbeta partials, which a fixed-order fold
