@@ -372,17 +372,6 @@ static bool pstrip_launch(int path, void (*kernel)(KArgs...), bool* attr_done, l
     }
 
 // deep-staged variants (groupnorm_dstrip.cuh)
-#define DSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
-    if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv) {                                              \
-        static bool done[64] = { false };                                                                   \
-        if (full) {                                                                                         \
-            static bool donef[64] = { false };                                                              \
-            return pstrip_launch(GN_PATH_DEEP, gn_fwd_dstrip<NTv, VPTv, ACT, MBv, true>, donef, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
-                gamma, beta, plan.g, eps, (int)grid);                                                       \
-        }                                                                                                   \
-        return pstrip_launch(GN_PATH_DEEP, gn_fwd_dstrip<NTv, VPTv, ACT, MBv, false>, done, pgrid, NTv, dsmem, s, y, mu, rstd, x, \
-            gamma, beta, plan.g, eps, (int)grid);                                                           \
-    }
 #define DSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
     if (plan.NT == NTv && plan.VPT == VPTv) {                                                               \
         static bool done[64] = { false };                                                                   \
@@ -600,9 +589,6 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 const long per_cta = (grid + resident - 1) / resident;
                 const long pgrid = (grid + per_cta - 1) / per_cta;
                 const bool full = plan.g.RSTEP * plan.VPT == HW;
-                // deep staging: half a strip more in flight, in the shared memory the plain pipeline leaves unused
-                const size_t dsmem = (size_t)(plan.VPT + plan.VPT / 2) * plan.NT * 16 + plan.smem;
-                // (measured on [256,32,32,256]: 2 % slower than the plain pipeline in forward, so off unless asked for)
                 // one barrier per strip
                 const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
                 const size_t osmem = (size_t)plan.VPT * plan.NT * 16
@@ -617,10 +603,6 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                     plan.g.stagger_lo = per_cta >= 8;  // paced stores in the kernels without activation
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
-                }
-                if (tune_get("gn_deep_fwd", 0) && dsmem * per_sm <= 226 * 1024 && grid >= 3 * pgrid) {
-                    DSTRIP_FWD_CASE(1024, 4, 1) DSTRIP_FWD_CASE(1024, 8, 1)
-                    DSTRIP_FWD_CASE(512, 4, 2) DSTRIP_FWD_CASE(512, 8, 2) DSTRIP_FWD_CASE(512, 8, 1)
                 }
                 PSTRIP_FWD_CASE(1024, 4, 1) PSTRIP_FWD_CASE(1024, 8, 1)
                 PSTRIP_FWD_CASE(512, 4, 2) PSTRIP_FWD_CASE(512, 8, 2) PSTRIP_FWD_CASE(512, 8, 1)

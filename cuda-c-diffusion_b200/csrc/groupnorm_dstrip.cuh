@@ -1,11 +1,11 @@
-// Deep-staged GroupNorm strip kernels (included by groupnorm.cu after groupnorm_strip.cuh).
+// Deep-staged GroupNorm backward strips (included by groupnorm.cu after groupnorm_strip.cuh).
 //
-// Same register-resident strips as gn_fwd_pstrip / gn_bwd_pstrip, with one change to the staging:
+// Same register-resident strips as gn_bwd_pstrip, with one change to the staging:
 // the pipelined kernels hold exactly ONE strip of asynchronous copies in flight per CTA, so from the
 // moment a strip has landed until its slots have been moved to registers and re-armed, the SM has no
 // load outstanding at all -- a dead window of ~0.7 us in every ~5 us strip period when one CTA owns an
-// SM.  Here part of each strip (the "head": all of x in backward, the first half of the rows in
-// forward) is double-buffered in the shared memory the pipelined kernels leave unused, so the head of
+// SM.  Here part of each strip (the "head": all of x) is double-buffered in the shared memory the
+// pipelined kernel leaves unused, so the head of
 // strip i+2 is already in flight while strip i+1 is being consumed: 1.5 strips of loads per CTA
 // instead of 1, never zero.  Every slot is re-armed immediately after it has been read (the copy for a
 // slot is issued right behind the shared-memory load that frees it), not after the whole strip.
@@ -13,6 +13,8 @@
 // cp.async groups, oldest first, when an iteration starts: head(i), tail(i), head(i+1); waiting for
 // all but the newest group gives strip i.  The iteration then commits tail(i+1) and head(i+2).
 // A thread only ever reads the slots it staged itself, so no barrier guards the staging buffers.
+// (The forward counterpart, half of each strip double-buffered, was 2-3 % slower than the plain
+// pipeline in every variant and is gone.)
 #pragma once
 
 namespace b200 {
@@ -24,148 +26,6 @@ __device__ __forceinline__ size_t dstrip_item_offset(const StripGeom& g, int ite
 {
     const int ctile = item % g.nct, b = item / g.nct;
     return (size_t)b * g.HW * g.C + (size_t)ctile * g.Ct + rowoff;
-}
-
-// ---------------------------------------------------------------------------
-// forward.  Slots j < HEAD are double-buffered (head[2][HEAD][NT]), the rest single (tail[VPT-HEAD][NT]).
-// dynamic smem = (VPT + HEAD) * NT * 16 bytes | red | chan | gstat
-// ---------------------------------------------------------------------------
-template <int NT, int VPT, int ACT, int MB, bool FULL>
-__global__ void __launch_bounds__(NT, MB) gn_fwd_dstrip(float* __restrict__ y, float* __restrict__ mu,
-    float* __restrict__ rstd, const float* __restrict__ x, const float* __restrict__ gamma,
-    const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
-{
-    pdl_prologue();
-    constexpr int HEAD = VPT / 2;
-    extern __shared__ float4 strip_stage[];
-    float4* head = strip_stage;                   // [2][HEAD][NT]
-    float4* tail = head + 2 * HEAD * NT;          // [VPT-HEAD][NT]
-    float* red = reinterpret_cast<float*>(tail + (VPT - HEAD) * NT);
-    const int red_floats = (g.Q <= 32 && 32 % g.Q == 0) ? 2 * (NT / 32) * g.Ct : 2 * NT * 4;
-    float* chan = red + red_floats;
-    float* gstat = chan + 2 * g.Ct;
-    const int t = threadIdx.x;
-    const int q = t % g.Q, rl = t / g.Q;
-    const int cb = 4 * q;
-    const int g0 = (cb + 0) / g.cpg, g1 = (cb + 1) / g.cpg, g2 = (cb + 2) / g.cpg, g3 = (cb + 3) / g.cpg;
-    const size_t rowoff = (size_t)rl * g.C + cb;
-    const size_t jstride = (size_t)g.RSTEP * g.C;
-    const int G = gridDim.x;
-
-    int item = blockIdx.x;
-    // prologue: head(0), tail(0), head(1)
-    {
-        const float* s0 = x + dstrip_item_offset(g, item < nitems ? item : 0, rowoff);
-        if (item < nitems) {
-#pragma unroll
-            for (int j = 0; j < HEAD; ++j)
-                if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&head[j * NT + t], s0 + j * jstride);
-        }
-        cp_async_commit();
-        if (item < nitems) {
-#pragma unroll
-            for (int j = HEAD; j < VPT; ++j)
-                if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&tail[(j - HEAD) * NT + t], s0 + j * jstride);
-        }
-        cp_async_commit();
-        if (item + G < nitems) {
-            const float* s1 = x + dstrip_item_offset(g, item + G, rowoff);
-#pragma unroll
-            for (int j = 0; j < HEAD; ++j)
-                if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&head[(HEAD + j) * NT + t], s1 + j * jstride);
-        }
-        cp_async_commit();
-    }
-    int par = 0;
-    for (; item < nitems; item += G, par ^= 1) {
-        const int ctile = item % g.nct, b = item / g.nct;
-        const int c0 = ctile * g.Ct;
-        const size_t base = (size_t)b * g.HW * g.C + c0 + cb;
-        const float4 K = __ldg(reinterpret_cast<const float4*>(x + base));
-        const bool more1 = item + G < nitems, more2 = item + 2 * G < nitems;
-        const float* n1 = x + dstrip_item_offset(g, more1 ? item + G : item, rowoff);
-        const float* n2 = x + dstrip_item_offset(g, more2 ? item + 2 * G : item, rowoff);
-        float4* hd = head + par * HEAD * NT;
-        cp_async_wait_but_one();
-        float4 v[VPT];
-#pragma unroll
-        for (int j = HEAD; j < VPT; ++j) {  // tail slots: read, then re-arm with strip i+1
-            const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            v[j] = live ? tail[(j - HEAD) * NT + t] : K;
-            if (more1 && live)
-                cp_async16(&tail[(j - HEAD) * NT + t], n1 + j * jstride);
-        }
-        cp_async_commit();
-#pragma unroll
-        for (int j = 0; j < HEAD; ++j) {    // head slots of this parity: read, then re-arm with strip i+2
-            const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            v[j] = live ? hd[j * NT + t] : K;
-            if (more2 && live)
-                cp_async16(&hd[j * NT + t], n2 + j * jstride);
-        }
-        cp_async_commit();
-
-        float4 s1, s2;
-        {
-            const f32x2 nk01 = pk(-K.x, -K.y), nk23 = pk(-K.z, -K.w);
-            f32x2 a1 = 0ull, b1 = 0ull, a2 = 0ull, b2 = 0ull;  // packed zeros
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const f32x2 d01 = pk_add(pk(v[j].x, v[j].y), nk01), d23 = pk_add(pk(v[j].z, v[j].w), nk23);
-                a1 = pk_add(a1, d01);
-                b1 = pk_add(b1, d23);
-                a2 = pk_fma(d01, d01, a2);
-                b2 = pk_fma(d23, d23, b2);
-            }
-            unpk(a1, s1.x, s1.y);
-            unpk(b1, s1.z, s1.w);
-            unpk(a2, s2.x, s2.y);
-            unpk(b2, s2.z, s2.w);
-        }
-        strip_fold<NT>(red, chan, g.Q, g.Ct, q, rl, s1, s2);
-        if (t < g.Gt) {
-            const float n = (float)g.HW * (float)g.cpg;
-            const float* xrow0 = x + (size_t)b * g.HW * g.C + c0 + t * g.cpg;
-            float msum = 0.0f;
-            for (int cl = 0; cl < g.cpg; ++cl)
-                msum += chan[t * g.cpg + cl] + (float)g.HW * __ldg(xrow0 + cl);
-            const float mean = msum / n;
-            float m2 = 0.0f;
-            for (int cl = 0; cl < g.cpg; ++cl) {
-                const int ch = t * g.cpg + cl;
-                const float dk = __ldg(xrow0 + cl) - mean;
-                m2 += chan[g.Ct + ch] + 2.0f * dk * chan[ch] + (float)g.HW * dk * dk;
-            }
-            const float rs = rsqrtf(m2 / n + eps);
-            gstat[t] = mean;
-            gstat[g.Gt + t] = rs;
-            mu[b * g.G + c0 / g.cpg + t] = mean;
-            rstd[b * g.G + c0 / g.cpg + t] = rs;
-        }
-        __syncthreads();
-        const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma + c0) + q);
-        const float4 be = __ldg(reinterpret_cast<const float4*>(beta + c0) + q);
-        float4 sc, sh;
-        sc.x = ga.x * gstat[g.Gt + g0]; sh.x = be.x - gstat[g0] * sc.x;
-        sc.y = ga.y * gstat[g.Gt + g1]; sh.y = be.y - gstat[g1] * sc.y;
-        sc.z = ga.z * gstat[g.Gt + g2]; sh.z = be.z - gstat[g2] * sc.z;
-        sc.w = ga.w * gstat[g.Gt + g3]; sh.w = be.w - gstat[g3] * sc.w;
-        const f32x2 sc01 = pk(sc.x, sc.y), sc23 = pk(sc.z, sc.w), sh01 = pk(sh.x, sh.y), sh23 = pk(sh.z, sh.w);
-        float* yrow = y + base + (size_t)rl * g.C;
-#pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            if (FULL || rl + j * g.RSTEP < g.HW) {
-                float4 o;
-                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].x, v[j].y), sc01, sh01)), o.x, o.y);
-                unpk(act_value_x2<ACT>(pk_fma(pk(v[j].z, v[j].w), sc23, sh23)), o.z, o.w);
-                __stcs(reinterpret_cast<float4*>(yrow + j * jstride), o);
-            }
-        }
-    }
-    cp_async_wait_all();
 }
 
 // ---------------------------------------------------------------------------

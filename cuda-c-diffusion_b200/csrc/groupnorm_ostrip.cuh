@@ -136,8 +136,8 @@ __device__ __forceinline__ void ostrip_group_total(const float* rg, const OStrip
 }
 
 // ---------------------------------------------------------------------------
-// forward: one strip staged ahead (staging a second strip half ahead, as gn_fwd_dstrip does, measured 3 % slower
-// with and without clusters).
+// forward: one strip staged ahead (staging half of a second strip as well, the way the backward double-buffers x,
+// measured 3 % slower with and without clusters).
 // dynamic smem = stage[VPT][NT] float4 | kst[GPT][NT] | gamma[C] | beta[C] | redg[2][Gt][2*NW+4]
 //
 // Launched as clusters of 4 CTAs where that applies (1024-thread CTAs, many strips each, strips per sample a
