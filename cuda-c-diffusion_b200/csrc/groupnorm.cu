@@ -239,7 +239,7 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
                 StripGeom g;
                 g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = rstep;
                 g.Gt = Ct / cpg; g.nct = C / Ct;
-                g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+                g.paced = 0;
                 out->g = g;
                 const int red = (Q <= 32 && 32 % Q == 0) ? 2 * (NT / 32) * Ct : 2 * NT * 4;
                 out->smem = (size_t)(red + 2 * Ct + 2 * g.Gt) * sizeof(float);
@@ -248,16 +248,6 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
     }
     if (best < 0)
         return false;
-    // Start the second CTA of every SM half a strip period later (only the first wave needs it:
-    // later CTAs inherit the phase of the slot they replace).
-    const long grid = (long)B * out->g.nct;
-    const int per_sm = ctas_per_sm_hint > 0 ? ctas_per_sm_hint : (out->NT <= 256 ? 4 : (out->NT <= 512 ? 2 : 1));
-    const int ns = tune_get("gn_stagger_ns", 0);  // measured: no effect on B200, so off unless requested
-    if (per_sm >= 2 && grid > (long)sm_count() * per_sm && ns > 0) {
-        out->g.stagger_lo = sm_count();
-        out->g.stagger_hi = sm_count() * 2;
-        out->g.stagger_ns = ns;
-    }
     return true;
 }
 
@@ -467,7 +457,7 @@ static bool exact7_plan(StripPlan* out, int HW, int C, int G, int NT)
         StripGeom g;
         g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = NT / Q;
         g.Gt = Ct / cpg; g.nct = C / Ct;
-        g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+        g.paced = 0;
         out->NT = NT;
         out->VPT = 7;
         out->g = g;
@@ -512,7 +502,8 @@ static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, 
     if (osmem * per_sm > 226 * 1024)
         return false;
     const bool full = true;
-    plan.g.stagger_lo = per_cta >= 8;  // paced stores in the kernels without activation
+    plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
+    // (clusters of 4 as for the 1024-thread strips: [256,28,28,256] 0.83 -> 0.80, so none here)
     OSTRIP_FWD_CASE(896, 7, 1) OSTRIP_FWD_CASE(448, 7, 2)
     return false;
 }
@@ -597,10 +588,10 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 if (gpt && osmem * per_sm <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min_fwd", 3)) {
                     // clusters of 4 neighbouring strips, staged in step (see gn_fwd_ostrip)
                     const int cw = tune_get("gn_fwd_cluster", 4);
-                    const bool clustered = cw > 1 && per_sm == 1 && (full || tune_get("gn_fwd_cluster_ragged", 0)) && plan.g.nct % cw == 0
-                        && per_cta >= tune_get("gn_fwd_cluster_min", 8);
+                    // (ragged strips, 28 x 28 in 1024 slots, lose from it: 0.66 -> 0.58)
+                    const bool clustered = cw > 1 && per_sm == 1 && full && plan.g.nct % cw == 0 && per_cta >= 8;
                     ClusterScope cluster(clustered ? cw : 1);
-                    plan.g.stagger_lo = per_cta >= 8;  // paced stores in the kernels without activation
+                    plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
                 }
@@ -703,7 +694,7 @@ static bool cstrip_plan(StripPlan* out, int HW, int C, int G)
     StripGeom g;
     g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = best; g.Q = best / 4; g.RSTEP = NT / g.Q;
     g.Gt = best / cpg; g.nct = C / best;
-    g.stagger_lo = g.stagger_hi = g.stagger_ns = 0;
+    g.paced = 0;
     out->NT = NT;
     out->VPT = 0;
     out->g = g;

@@ -179,8 +179,8 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
     // [256,32,32,256]; a fixed 250 ns between row blocks: 0.91).  So there each row block's store waits until one
     // more row block of the NEXT strip has landed: stores leave at the rate at which loads arrive.  With SiLU the
     // arithmetic already paces the stores and the same scheme costs 5 %.
-    // Only for launches with many strips per CTA (the host sets g.stagger_lo): with 2-4 strips the waits cost more.
-    const bool paced = ACT == ACT_IDENTITY && VPT <= 8 && g.stagger_lo != 0;
+    // Only for launches with many strips per CTA (the host sets g.paced): with 2-4 strips the waits cost more.
+    const bool paced = ACT == ACT_IDENTITY && VPT <= 8 && g.paced != 0;
 
     for (int i = t; i < g.C / 4; i += NT) {
         reinterpret_cast<float4*>(gsm)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);

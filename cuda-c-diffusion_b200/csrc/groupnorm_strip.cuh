@@ -81,9 +81,9 @@ __device__ __forceinline__ void strip_fold(float* red, float* chan, int Q, int C
 
 struct StripGeom {
     int HW, C, G, cpg, Ct, Q, RSTEP, Gt, nct;
-    // CTAs with stagger_lo <= blockIdx.x < stagger_hi start stagger_ns later, so that the CTAs
-    // sharing an SM run out of phase (one loads while the other computes and stores)
-    int stagger_lo, stagger_hi, stagger_ns;
+    int paced;  // one-barrier forward without activation: release stores as the next strip's loads land
+    // (Starting the second CTA of every SM half a strip period late, so that the two run out of phase, was
+    // measured: no effect.)
 };
 
 // ---------------------------------------------------------------------------
@@ -105,8 +105,6 @@ __global__ void __launch_bounds__(NT, (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))) gn_
     const int c0 = ctile * g.Ct;
     const int q = t % g.Q, rl = t / g.Q;
     const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
-    if ((int)blockIdx.x >= g.stagger_lo && (int)blockIdx.x < g.stagger_hi)
-        __nanosleep(g.stagger_ns);
 
     // per-channel shift K = row 0 of the sample (same for every thread of a column)
     const float4 K = __ldg(reinterpret_cast<const float4*>(x + base));
@@ -202,8 +200,6 @@ __global__ void __launch_bounds__(NT, MB) gn_bwd_strip(float* __restrict__ dx,
     const int q = t % g.Q, rl = t / g.Q;
     const size_t base = (size_t)b * g.HW * g.C + c0 + 4 * q;
     const int cb = 4 * q;
-    if ((int)blockIdx.x >= g.stagger_lo && (int)blockIdx.x < g.stagger_hi)
-        __nanosleep(g.stagger_ns);
     const int gl0 = (cb + 0) / g.cpg, gl1 = (cb + 1) / g.cpg, gl2 = (cb + 2) / g.cpg, gl3 = (cb + 3) / g.cpg;
 
     float4 xv[VPT], dv[VPT];
