@@ -5,14 +5,14 @@
 // The matrices are small (<= ~600 KB), so the op is latency-bound: what counts is
 // how few dependent memory round trips a launch needs and how many matrices one
 // launch covers.  Cluster kernel: a cluster of CS CTAs splits the `in` rows of a
-// 32-column strip; each thread keeps its <= 8 float4 of the strip in registers
+// 32-column strip; each thread keeps its <= 12 float4 of the strip in registers
 // (single read of W), column sums of squares are folded in shared memory and
 // then across the cluster through distributed shared memory, and the scaled
 // values are written straight from registers.  A table of matrices lets one
 // launch normalise every MP weight of a model, forward and backward; hosts whose
 // modules call the per-weight launchers can have those calls recorded once and
 // then batched (b200_wn_batch_mode).
-// Shapes outside the cluster kernel's limits (out % 4 != 0, in > 2048,
+// Shapes outside the cluster kernel's limits (out % 4 != 0, in > 3072,
 // misaligned) use the strip kernel (two sweeps, any shape).
 #include "dev_common.cuh"
 #include "../../include/b200_layer_kernels.h"
@@ -27,8 +27,8 @@ namespace b200 {
 
 constexpr int WN_THREADS = 256;
 constexpr int WN_COLS = 32;       // columns per strip
-constexpr int WN_VMAX = 8;        // float4 per thread -> at most 256 rows per CTA
-constexpr int WN_MAX_ROWS = 2048; // 8 CTAs x 256 rows
+constexpr int WN_VMAX = 12;       // float4 per thread -> at most 384 rows per CTA
+constexpr int WN_MAX_ROWS = 3072; // 8 CTAs x 384 rows (3x3 convolutions of 256 input channels: 2304)
 
 struct WnTable {
     float* W[B200_MAX_MULTI];
@@ -222,6 +222,33 @@ __global__ void __launch_bounds__(WN_THREADS) wn_backward_cluster(const WnGradTa
     cluster.sync();
 }
 
+// Narrow matrices (a handful of output columns, e.g. the last convolution of a UNet with one image channel):
+// one CTA per column, its 256 threads stride over the rows.  The strip kernel below would leave 8 threads of one
+// CTA walking the whole column twice (24 us for [576, 1]).
+// MODE 0: forward.  MODE 1: backward.
+template <int MODE>
+__global__ void __launch_bounds__(256) wn_column(float* __restrict__ A, const float* __restrict__ Wn,
+    const float* __restrict__ gain, float* __restrict__ g_gain, int in, int out, float eps)
+{
+    pdl_prologue();
+    __shared__ float buf[32];
+    const int col = blockIdx.x;
+    float acc = 0.0f;
+    for (int r = threadIdx.x; r < in; r += 256) {
+        const float a = A[(size_t)r * out + col];
+        acc += MODE == 0 ? a * a : a * Wn[(size_t)r * out + col];
+    }
+    const float tot = cta_sum(acc, buf);
+    if (MODE == 1 && threadIdx.x == 0)
+        atomicAdd(g_gain, tot);
+    const float cv = MODE == 0 ? rsqrtf(tot + eps) : tot;
+    const float gn = MODE == 1 ? gain[0] : 0.0f;
+    for (int r = threadIdx.x; r < in; r += 256) {
+        const size_t k = (size_t)r * out + col;
+        A[k] = MODE == 0 ? A[k] * cv : gn * (A[k] - cv * Wn[k]);
+    }
+}
+
 // Strip kernel for any shape: block = 32 columns x 8 row lanes, two sweeps.
 // MODE 0: forward.  MODE 1: backward.
 template <int MODE>
@@ -381,7 +408,10 @@ static void weight_normalize_now(float* W, int in, int out, float eps, cudaStrea
         wn_launch_cluster_fwd(tb, wn_cluster_size(in), eps, s);
         return;
     }
-    launch_k(wn_strip<0>, (out + 31) / 32, dim3(32, 8), 0, s, W, nullptr, nullptr, nullptr, in, out, eps);
+    if (out <= 8)
+        launch_k(wn_column<0>, out, 256, 0, s, W, nullptr, nullptr, nullptr, in, out, eps);
+    else
+        launch_k(wn_strip<0>, (out + 31) / 32, dim3(32, 8), 0, s, W, nullptr, nullptr, nullptr, in, out, eps);
     count_launch();
     B200_CHECK_LAUNCH();
 }
@@ -430,7 +460,10 @@ static void weight_normalize_backward_now(float* gW, const float* Wn, const floa
         wn_launch_cluster_bwd(tb, wn_cluster_size(in), s);
         return;
     }
-    launch_k(wn_strip<1>, (out + 31) / 32, dim3(32, 8), 0, s, gW, Wn, gain, g_gain, in, out, 0.0f);
+    if (out <= 8)
+        launch_k(wn_column<1>, out, 256, 0, s, gW, Wn, gain, g_gain, in, out, 0.0f);
+    else
+        launch_k(wn_strip<1>, (out + 31) / 32, dim3(32, 8), 0, s, gW, Wn, gain, g_gain, in, out, 0.0f);
     count_launch();
     B200_CHECK_LAUNCH();
 }

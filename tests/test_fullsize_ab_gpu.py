@@ -170,6 +170,17 @@ def test_edm_op_set_256x28x28x128(lib, ref_lib):
     _ab(lib, ref_lib, "weight_norm", dict(rows=1152, cols=128, eps=1e-4), wn, "cfg2/weight_norm")
 
 
+@pytest.mark.parametrize("rows,cols", [(2304, 128), (2304, 256), (3072, 64), (3080, 64), (576, 1), (576, 3), (27, 8)])
+def test_weight_norm_shapes_of_the_unets(lib, ref_lib, rows, cols):
+    """Weights beyond the benchmark's [1152,128]: 3x3 convolutions over 256 input channels (cluster kernel with 9-12
+    register slots per thread), one row more than the cluster kernel holds (strip kernel), and the narrow
+    matrices of a UNet's last convolution (one CTA per column)."""
+    import torch
+    g = _gen(7)
+    wn = dict(W=_randn(g, rows, cols), M=_randn(g, rows, cols), gain=torch.full((1,), 1.3, device="cuda"))
+    _ab(lib, ref_lib, "weight_norm", dict(rows=rows, cols=cols, eps=1e-4), wn, f"weight_norm[{rows},{cols}]")
+
+
 def test_ddpm_block_kernels_256x32x32x256(lib, ref_lib):
     """Configuration 3: GroupNorm(32)+affine+SiLU (fused here; GroupNorm then SiLU in the reference, as
     conv_residual.c:28-29,51-52 composes them) and LayerNorm over C=256 on the same tensor viewed as
