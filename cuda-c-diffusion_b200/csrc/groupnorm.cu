@@ -300,14 +300,19 @@ static bool strip_launch(int path, void (*kernel)(KArgs...), long grid, int NT, 
             if (nclusters == 0) {
                 if (cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess || nclusters < 1) {
                     (void)cudaGetLastError();
-                    return false;
+                    nclusters = -1;  // no cluster of this shape fits this device (or partition)
                 }
                 if (nknown < 32)
                     known[nknown++] = Known{ (const void*)kernel, dev, w, NT, nclusters, smem };
             }
         }
-        if ((long)nclusters * w < (long)cfg.gridDim.x)
+        if (nclusters < 1) {
+            // plain CTAs instead: the kernels find a cluster of one and skip the cluster barrier
+            --nat;
+            cfg.gridDim.x = (unsigned)grid;
+        } else if ((long)nclusters * w < (long)cfg.gridDim.x) {
             cfg.gridDim.x = (unsigned)(nclusters * w);
+        }
     }
     cfg.attrs = at;
     cfg.numAttrs = nat;
