@@ -98,7 +98,9 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // not one of these kernels (cuBLAS, a copy) simply completes first, as in an ordinary launch; inside
 // stream capture the dependency becomes a programmatic edge of the graph.
 // Large launches are excluded because there it costs: back to back, the four big kernels of the
-// benchmark step ([256,32,32,256]) take 0.485-0.490 ms with the attribute and 0.456-0.460 ms without.
+// benchmark step ([256,32,32,256]) take 0.485-0.490 ms with the attribute and 0.456-0.460 ms without
+// (0.442 ms with this size rule; 0.452-0.459 ms when large grids also hold back the release of their
+// dependents until their CTAs exit).
 // (The likely cause: CTAs of a dependent grid are placed on SMs in the order in which the predecessor
 // frees them rather than all at once, and the bandwidth the strided kernels reach depends on which CTAs
 // run side by side -- see groupnorm_ostrip.cuh.)
