@@ -841,9 +841,9 @@ def main():
             # arm once as a plain drop-in at the launch_* ABI and once with the fused residual block linked in
             if not args.no_trainer:
                 if args.impl == "b200":
-                    ddpm = {"drop_in": edm_train_images_per_s(BIN / "ddpm_demo_b200", steps=(50, 350),
+                    ddpm = {"drop_in": edm_train_images_per_s(BIN / "ddpm_demo_b200", steps=(100, 700),
                                                               write_config=write_ddpm_config),
-                            "fused_block": edm_train_images_per_s(BIN / "ddpm_demo_b200_fused", steps=(50, 350),
+                            "fused_block": edm_train_images_per_s(BIN / "ddpm_demo_b200_fused", steps=(100, 700),
                                                                   write_config=write_ddpm_config)}
                 else:
                     ddpm = edm_train_images_per_s(ROOT / "oracle" / "_ref" / "ddpm_demo_ref", steps=(20, 120),
