@@ -541,6 +541,8 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             }
             orow += jstride;
         }
+        // (sharing this fold among all threads -- NW lanes per sum, xor shuffles -- instead of leaving it to Ct
+        // threads of warp 0: backward 137 -> 153 us on [256,32,32,256])
         if (t < g.Ct) {  // one partial row per sample: [b][0:C] dgamma, [b][C:2C] dbeta
             const float* rcf = reinterpret_cast<const float*>(rc);
             float sa = 0.0f, sb = 0.0f;
