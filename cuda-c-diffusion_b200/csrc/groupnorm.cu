@@ -503,7 +503,7 @@ static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, 
     const long pgrid = (grid + per_cta - 1) / per_cta;
     const int gpt = ostrip_gpt(plan.g);
     const size_t osmem = (size_t)plan.VPT * plan.NT * 16
-        + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * (plan.NT / 32) + 4)) * sizeof(float);
+        + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(plan.NT / 32)) * sizeof(float);
     if (osmem * per_sm > 226 * 1024)
         return false;
     const bool full = true;
@@ -543,7 +543,7 @@ static bool gn_backward_exact7(float* dx, float* dgamma, float* dbeta, const flo
     }
     const int gpt = ostrip_gpt(plan.g), nw = plan.NT / 32;
     const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
-        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * nw + 4)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16;
+        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16;
     if (osmem > 226 * 1024)
         return false;
     Scratch sc;
@@ -588,7 +588,7 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                 // one barrier per strip
                 const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
                 const size_t osmem = (size_t)plan.VPT * plan.NT * 16
-                    + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * (plan.NT / 32) + 4)) * sizeof(float);
+                    + (size_t)(gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(plan.NT / 32)) * sizeof(float);
                 // (with few strips per CTA the longer set-up of these kernels costs more than the barriers save)
                 if (gpt && osmem * per_sm <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min_fwd", 3)) {
                     // clusters of 4 neighbouring strips, staged in step (see gn_fwd_ostrip)
@@ -659,7 +659,7 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                 const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
                 const int nw = plan.NT / 32;
                 const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
-                    + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * (2 * nw + 4)) * sizeof(float)
+                    + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float)
                     + (size_t)2 * nw * 2 * plan.g.Q * 16;
                 // (a cluster barrier per strip, as in the forward kernel, was measured here too: 0.89 -> 0.78 with
                 // pairs, worse with wider clusters -- the backward has no idle time to absorb the lock step)

@@ -38,6 +38,11 @@
 
 namespace b200 {
 
+// Floats per group row of the per-warp partial sums: NW float2 plus padding such that the rows of different
+// groups never start on the same bank (a stride of exactly 32 floats, NW = 14, cost the backward of
+// [256,28,28,128] 10 %: four groups per warp read their rows at once).
+__host__ __device__ constexpr int ostrip_row_floats(int nw) { return (2 * nw + 4) | 4; }
+
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
@@ -135,10 +140,27 @@ __device__ __forceinline__ void ostrip_group_total(const float* rg, const OStrip
     second = b;
 }
 
+// The same total with no shuffles: every lane reads all NW per-warp partials of its group (broadcast 128-bit loads)
+// and adds them in a fixed order.  For the backward kernels (16 warps, shared-memory and shuffle queue already the
+// busiest unit): fewer queue entries than the lane-split form.
+template <int NW>
+__device__ __forceinline__ void ostrip_group_total_direct(const float* rg, float& first, float& second)
+{
+    float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+#pragma unroll
+    for (int w = 0; w < NW; w += 2) {
+        const float4 p = *reinterpret_cast<const float4*>(rg + 2 * w);
+        a0.x += p.x; a0.y += p.y;
+        a1.x += p.z; a1.y += p.w;
+    }
+    first = a0.x + a1.x;
+    second = a0.y + a1.y;
+}
+
 // ---------------------------------------------------------------------------
 // forward: one strip staged ahead (staging half of a second strip as well, the way the backward double-buffers x,
 // measured 3 % slower with and without clusters).
-// dynamic smem = stage[VPT][NT] float4 | kst[GPT][NT] | gamma[C] | beta[C] | redg[2][Gt][2*NW+4]
+// dynamic smem = stage[VPT][NT] float4 | kst[GPT][NT] | gamma[C] | beta[C] | redg[2][Gt][ostrip_row_floats(NW)]
 //
 // Launched as clusters of 4 CTAs where that applies (1024-thread CTAs, many strips each, strips per sample a
 // multiple of 4): consecutive CTAs walk consecutive strips, i.e. neighbouring 128-byte column tiles of the SAME
@@ -154,7 +176,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 {
     pdl_prologue();
     constexpr int NW = NT / 32;
-    constexpr int RG = 2 * NW + 4;  // floats per group row (16 bytes of padding: rows of different groups on different banks)
+    constexpr int RG = ostrip_row_floats(NW);
     extern __shared__ float4 strip_stage[];
     float4* stage = strip_stage;
     float* kst = reinterpret_cast<float*>(stage + VPT * NT);  // slot [k][t]: shift of this thread's group k
@@ -339,7 +361,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 // ---------------------------------------------------------------------------
 // backward (deep-staged: x double-buffered, dy single-buffered, as in gn_bwd_dstrip).
 // dynamic smem = xs[2][VPT][NT] float4 | ds[VPT][NT] float4 | mst[2*GPT][NT] | gamma[C] | beta[C]
-//              | redg[2][Gt][2*NW+4] | redc[2][NW][2][Q] float4
+//              | redg[2][Gt][ostrip_row_floats(NW)] | redc[2][NW][2][Q] float4
 // ---------------------------------------------------------------------------
 template <int NT, int VPT, int ACT, bool FULL, int GPT>
 __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, float* __restrict__ partials,
@@ -349,7 +371,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 {
     pdl_prologue();
     constexpr int NW = NT / 32;
-    constexpr int RG = 2 * NW + 4;
+    constexpr int RG = ostrip_row_floats(NW);
     extern __shared__ float4 strip_stage[];
     float4* xs = strip_stage;
     float4* ds = xs + 2 * VPT * NT;
@@ -523,8 +545,12 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
         float mgv[GPT], mgxv[GPT];
 #pragma unroll
         for (int k = 0; k < GPT; ++k) {
-            float hi, lo, second;
-            ostrip_group_total<NW, false>(rg + (gl + k) * RG, ln, g.Q, M, hi, lo, second);
+            float hi, lo = 0.0f, second;
+            if constexpr (NW % 2 == 0 && NW <= 16)
+                ostrip_group_total_direct<NW>(rg + (gl + k) * RG, hi, second);
+            else
+                ostrip_group_total<NW, false>(rg + (gl + k) * RG, ln, g.Q, M, hi, lo, second);
+            (void)lo;
             mgv[k] = hi * inv_n;
             mgxv[k] = second * inv_n;
         }
