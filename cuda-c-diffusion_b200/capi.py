@@ -89,6 +89,7 @@ SIGNATURES = {
     "b200_launch_count": "",
     "b200_launch_count_reset": "",
     "b200_groupnorm_path_count": "i",
+    "b200_groupnorm_describe": "iiiiiihi",
     "b200_scratch_reserve": "sq",
     "b200_tune_set": "hi",
     "b200_tune_get": "hi",
@@ -104,6 +105,7 @@ RETURNS = {
     "b200_device_error_status": ctypes.c_int,
     "b200_launch_count": ctypes.c_longlong,
     "b200_groupnorm_path_count": ctypes.c_longlong,
+    "b200_groupnorm_describe": ctypes.c_int,
     "b200_scratch_reserve": ctypes.c_int,
     "b200_tune_get": ctypes.c_int,
     "b200_version": ctypes.c_char_p,

@@ -83,6 +83,10 @@ bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out);
 // go to out_a, the rest to out_b (rownorm.cu).
 void fold_partials(float* out_a, float* out_b, const float* partials, int nparts, int width, int split,
     cudaStream_t s);
+// Set (per thread) while b200_groupnorm_describe walks the dispatcher: launch helpers then record what they would
+// launch instead of launching, scratch_get hands out nothing, fold_partials does nothing.  No CUDA call is made.
+bool planning_only();
+void planning_only_set(bool on);
 // Device address of the error word that kernels set when a bounded wait runs
 // out (0 = healthy); one word per device.
 int* device_error_word();

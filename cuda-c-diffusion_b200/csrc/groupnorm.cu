@@ -251,17 +251,45 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
     return true;
 }
 
+// What the dispatcher decided, recorded in planning-only mode (b200_groupnorm_describe).
+struct PlannedLaunch {
+    int path, nt, ct, rows_per_cta, cluster;
+    long grid;
+    size_t smem;
+};
+static thread_local PlannedLaunch t_planned;
+
+template <class T>
+static inline void note_geometry(const T&) {}
+static inline void note_geometry(const StripGeom& g)
+{
+    t_planned.ct = g.Ct;
+    t_planned.rows_per_cta = g.RSTEP;  // rows per register slot; the kernel's slot count is part of its name
+}
+
 // Cluster width for the next strip launch of this thread (1 = no cluster); with a width above 1 the grid is
 // cut to the clusters the device can hold at once (the kernels are persistent: fewer CTAs walk more strips).
 static thread_local int t_gn_cluster = 1;
 struct ClusterScope {
-    explicit ClusterScope(int w) { t_gn_cluster = w; }
+    explicit ClusterScope(int w)
+    {
+        t_gn_cluster = w;
+        t_planned.cluster = w;
+    }
     ~ClusterScope() { t_gn_cluster = 1; }
 };
 
 template <class... KArgs, class... Args>
 static bool strip_launch(int path, void (*kernel)(KArgs...), long grid, int NT, size_t smem, cudaStream_t s, Args... args)
 {
+    if (planning_only()) {
+        t_planned.path = path;
+        t_planned.nt = NT;
+        t_planned.grid = grid;
+        t_planned.smem = smem;
+        (note_geometry(args), ...);
+        return true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3((unsigned)NT, 1, 1);
@@ -330,6 +358,8 @@ template <class... KArgs, class... Args>
 static bool pstrip_launch(int path, void (*kernel)(KArgs...), bool* attr_done, long grid, int NT, size_t smem, cudaStream_t s,
     Args... args)
 {
+    if (planning_only())
+        return strip_launch(path, kernel, grid, NT, smem, s, args...);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
         return false;
@@ -788,6 +818,12 @@ static void gn_forward(float* y, float* mu, float* rstd, const float* x, const f
         return;
     if (gn_forward_cstrip<ACT>(y, mu, rstd, x, gamma, beta, B, HW, C, G, eps, s))
         return;
+    if (planning_only()) {
+        t_planned.path = GN_PATH_GENERIC;
+        t_planned.nt = GN_GENERIC_THREADS;
+        t_planned.grid = (long)B * G;
+        return;
+    }
     gn_path(GN_PATH_GENERIC, true);
     launch_k(gn_fwd_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, y, mu, rstd, x, gamma, beta, HW, C, G, eps);
     count_launch();
@@ -806,6 +842,12 @@ static void gn_backward(float* dx, float* dgamma, float* dbeta, const float* dy,
     Scratch sc;
     B200_REQUIRE(scratch_get(s, (size_t)2 * B * C, 0, &sc), "groupnorm_backward: scratch allocation failed (the arena cannot grow during stream capture: call b200_scratch_reserve before capturing)");
     B200_REQUIRE(B <= 65535, "groupnorm_backward: batch %d too large for the generic path", B);
+    if (planning_only()) {
+        t_planned.path = GN_PATH_GENERIC;
+        t_planned.nt = GN_GENERIC_THREADS;
+        t_planned.grid = (long)B * G;
+        return;
+    }
     gn_path(GN_PATH_GENERIC, true);
     launch_k(gn_bwd_dx_generic<ACT>, B * G, GN_GENERIC_THREADS, 0, s, dx, dy, x, gamma, beta, mu, rstd, HW, C, G);
     count_launch();
@@ -879,6 +921,29 @@ void launch_groupnorm_act_backward(float* dx, float* ggamma, float* gbeta, const
     if (!gn_args_ok("groupnorm_act_backward", batch, HW, C, G) || batch == 0)
         return;
     GN_DISPATCH_ACT((int)act, (gn_backward<A>(dx, ggamma, gbeta, dy, x, gamma, beta, mu, rstd, batch, HW, C, G, s)));
+}
+
+int b200_groupnorm_describe(int batch, int HW, int C, int G, int act, int backward, char* out, int out_len)
+{
+    if (!out || out_len <= 0 || batch <= 0 || HW <= 0 || C <= 0 || G <= 0 || C % G != 0)
+        return -1;
+    static const char* const names[] = { "strip", "pipelined", "deep-staged", "one-barrier", "chunked", "generic" };
+    b200::t_planned = b200::PlannedLaunch();
+    b200::t_planned.path = -1;
+    b200::t_planned.cluster = 1;
+    b200::planning_only_set(true);
+    float* none = nullptr;
+    if (backward) {
+        GN_DISPATCH_ACT(act, (gn_backward<A>(none, none, none, none, none, none, none, none, none, batch, HW, C, G, nullptr)));
+    } else {
+        GN_DISPATCH_ACT(act, (gn_forward<A>(none, none, none, none, none, none, batch, HW, C, G, 1e-5f, nullptr)));
+    }
+    b200::planning_only_set(false);
+    const b200::PlannedLaunch& p = b200::t_planned;
+    if (p.path < 0 || p.path >= b200::GN_PATHS)
+        return -1;
+    return snprintf(out, (size_t)out_len, "family=%s threads=%d strip_channels=%d ctas=%ld cluster=%d smem=%zu", names[p.path],
+        p.nt, p.ct, p.grid, p.cluster, p.smem);
 }
 
 long long b200_groupnorm_path_count(int path)

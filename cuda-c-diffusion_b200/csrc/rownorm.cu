@@ -457,6 +457,8 @@ static inline bool fast_rows_ok(int C) { return C % 128 == 0 && C >= 128 && C <=
 void fold_partials(float* out_a, float* out_b, const float* partials, int nparts, int width, int split,
     cudaStream_t s)
 {
+    if (planning_only())
+        return;
     launch_k(fold_partials_kernel, (width + 31) / 32, dim3(32, 32), 0, s, out_a, out_b, partials, nparts, width, split);
     count_launch();
     B200_CHECK_LAUNCH();

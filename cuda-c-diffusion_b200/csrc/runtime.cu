@@ -134,8 +134,16 @@ static bool stream_is_capturing(cudaStream_t s)
     return cudaStreamIsCapturing(s, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
 }
 
+static thread_local bool t_planning_only = false;
+bool planning_only() { return t_planning_only; }
+void planning_only_set(bool on) { t_planning_only = on; }
+
 bool scratch_get(cudaStream_t s, size_t floats, size_t ntickets, Scratch* out)
 {
+    if (t_planning_only) {
+        *out = Scratch();
+        return true;
+    }
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess)
         return false;

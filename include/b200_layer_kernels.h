@@ -326,6 +326,12 @@ void b200_launch_count_reset(void);
    strips, 2 deep-staged strips, 3 one-barrier strips, 4 chunked strips, 5 generic; -1 for any other value.
    For tests that must know which family they exercised. */
 long long b200_groupnorm_path_count(int path);
+/* Which kernel family, CTA size, strip width, grid and cluster width the GroupNorm dispatcher would choose for
+   a shape, written as text ("family=one-barrier threads=1024 strip_channels=32 ctas=147 cluster=4 smem=...");
+   `act` as in launch_groupnorm_act_forward (0 = none), `backward` 0 or 1.  Makes no CUDA call and launches
+   nothing (without a device the SM count is taken as 148), so the dispatch rules can be tested on a CPU box.
+   Returns the length of the text, -1 for bad arguments.  Pointers are assumed 16-byte aligned. */
+int b200_groupnorm_describe(int batch, int HW, int C, int G, int act, int backward, char* out, int out_len);
 
 /* Pre-sizes the scratch arena used by the backward kernels on `s` so that no
    allocation happens later (call before capturing a CUDA graph). */
