@@ -573,7 +573,7 @@ static bool gn_backward_exact7(float* dx, float* dgamma, float* dbeta, const flo
     }
     const int gpt = ostrip_gpt(plan.g), nw = plan.NT / 32;
     const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
-        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16;
+        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0);
     if (osmem > 226 * 1024)
         return false;
     Scratch sc;
@@ -690,7 +690,7 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                 const int nw = plan.NT / 32;
                 const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
                     + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float)
-                    + (size_t)2 * nw * 2 * plan.g.Q * 16;
+                    + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0);
                 // (a cluster barrier per strip, as in the forward kernel, was measured here too: 0.89 -> 0.78 with
                 // pairs, worse with wider clusters -- the backward has no idle time to absorb the lock step)
                 if (gpt && per_sm == 1 && osmem <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min", 6)) {

@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 // ---------------------------------------------------------------------------
 // backward (deep-staged: x double-buffered, dy single-buffered, as in gn_bwd_dstrip).
 // dynamic smem = xs[2][VPT][NT] float4 | ds[VPT][NT] float4 | mst[2*GPT][NT] | gamma[C] | beta[C]
-//              | redg[2][Gt][ostrip_row_floats(NW)] | redc[2][NW][2][Q] float4
+//              | redg[2][Gt][ostrip_row_floats(NW)] | redc[2][NW][2][Q] float4 | wsum[NW][32][8] (Q == 4 only)
 // ---------------------------------------------------------------------------
 template <int NT, int VPT, int ACT, bool FULL, int GPT>
 __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, float* __restrict__ partials,
@@ -380,6 +380,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
     float* bsm = gsm + g.C;
     float* redg = bsm + g.C;
     float4* redc = reinterpret_cast<float4*>(redg + 2 * g.Gt * RG);
+    float* wsum = reinterpret_cast<float*>(redc + 2 * NW * 2 * g.Q);  // [NW][32][8], used when Q == 4
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int q = t % g.Q, rl = t / g.Q;
     const int cb = 4 * q;
@@ -509,35 +510,66 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             unpk(a2, sB.x, sB.y);
             unpk(b2, sB.z, sB.w);
         }
-        // per-warp channel sums (all lanes of a float4 column end up with them) ...
-        for (int off = g.Q; off < 32; off <<= 1) {
-            sA = shfl_xor4(sA, off);
-            sB = shfl_xor4(sB, off);
-        }
-        // ... and from them the gamma-weighted per-warp group sums
-        float sg[GPT], sgx[GPT];
-        if constexpr (GPT == 1) {
-            sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y) + fmaf(ga.z, sA.z, ga.w * sA.w);
-            sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y) + fmaf(ga.z, sB.z, ga.w * sB.w);
-            for (int off = 1; off < M; off <<= 1) {
-                sg[0] += __shfl_xor_sync(0xffffffffu, sg[0], off);
-                sgx[0] += __shfl_xor_sync(0xffffffffu, sgx[0], off);
-            }
-        } else {
-            sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y);
-            sg[GPT - 1] = fmaf(ga.z, sA.z, ga.w * sA.w);
-            sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y);
-            sgx[GPT - 1] = fmaf(ga.z, sB.z, ga.w * sB.w);
-        }
         float* rg = redg + par * g.Gt * RG;
         float4* rc = redc + (size_t)par * NW * 2 * g.Q;
-        if (lane < g.Q) {
-            rc[(warp * 2 + 0) * g.Q + q] = sA;
-            rc[(warp * 2 + 1) * g.Q + q] = sB;
-            if (writer) {
+        if (g.Q == 4) {
+            // The strip is 4 float4 columns wide, so a warp holds 8 row lanes of each column.  Instead of three
+            // rounds of eight shuffles, the warp transposes through shared memory: every lane stores its 8 partial
+            // sums, then lane (col, comp) adds the 8 row lanes of ONE of the 32 (column, component) sums with
+            // conflict-free 32-bit loads.  The shuffle / shared-memory queue is this kernel's busiest unit
+            // (28 entries per thread and strip become 15).
+            float* W = wsum + warp * 256;
+            *reinterpret_cast<float4*>(W + lane * 8) = sA;
+            *reinterpret_cast<float4*>(W + lane * 8 + 4) = sB;
+            __syncwarp();
+            const int col = lane >> 3, comp = lane & 7;
+            float v = 0.0f;
 #pragma unroll
-                for (int k = 0; k < GPT; ++k)
-                    *reinterpret_cast<float2*>(rg + (gl + k) * RG + 2 * warp) = make_float2(sg[k], sgx[k]);
+            for (int r = 0; r < 8; ++r)
+                v += W[(r * 4 + col) * 8 + comp];
+            float* rcf = reinterpret_cast<float*>(rc);
+            rcf[(warp * 2 + (comp >> 2)) * g.Ct + col * 4 + (comp & 3)] = v;  // comp < 4: sums of g, else of g * xhat
+            float gv = v * gsm[c0 + col * 4 + (comp & 3)];
+            gv += __shfl_xor_sync(0xffffffffu, gv, 1);
+            if constexpr (GPT == 1) {
+                gv += __shfl_xor_sync(0xffffffffu, gv, 2);
+                for (int off = 8; off < 8 * M; off <<= 1)
+                    gv += __shfl_xor_sync(0xffffffffu, gv, off);
+                if ((comp & 3) == 0 && (col & (M - 1)) == 0)
+                    rg[(col / M) * RG + 2 * warp + (comp >> 2)] = gv;
+            } else {
+                if ((comp & 1) == 0)
+                    rg[(col * 2 + ((comp >> 1) & 1)) * RG + 2 * warp + (comp >> 2)] = gv;
+            }
+        } else {
+            // per-warp channel sums (all lanes of a float4 column end up with them) ...
+            for (int off = g.Q; off < 32; off <<= 1) {
+                sA = shfl_xor4(sA, off);
+                sB = shfl_xor4(sB, off);
+            }
+            // ... and from them the gamma-weighted per-warp group sums
+            float sg[GPT], sgx[GPT];
+            if constexpr (GPT == 1) {
+                sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y) + fmaf(ga.z, sA.z, ga.w * sA.w);
+                sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y) + fmaf(ga.z, sB.z, ga.w * sB.w);
+                for (int off = 1; off < M; off <<= 1) {
+                    sg[0] += __shfl_xor_sync(0xffffffffu, sg[0], off);
+                    sgx[0] += __shfl_xor_sync(0xffffffffu, sgx[0], off);
+                }
+            } else {
+                sg[0] = fmaf(ga.x, sA.x, ga.y * sA.y);
+                sg[GPT - 1] = fmaf(ga.z, sA.z, ga.w * sA.w);
+                sgx[0] = fmaf(ga.x, sB.x, ga.y * sB.y);
+                sgx[GPT - 1] = fmaf(ga.z, sB.z, ga.w * sB.w);
+            }
+            if (lane < g.Q) {
+                rc[(warp * 2 + 0) * g.Q + q] = sA;
+                rc[(warp * 2 + 1) * g.Q + q] = sB;
+                if (writer) {
+#pragma unroll
+                    for (int k = 0; k < GPT; ++k)
+                        *reinterpret_cast<float2*>(rg + (gl + k) * RG + 2 * warp) = make_float2(sg[k], sgx[k]);
+                }
             }
         }
         __syncthreads();
