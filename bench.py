@@ -673,7 +673,7 @@ KERNEL_BYTES = {"gn_silu_fwd": 2 * NEL * 4, "gn_silu_bwd": 3 * NEL * 4, "ln_fwd"
 # (GroupNorm: captured at the full batch; LayerNorm: at batch 128 and scaled by 2, traffic grows linearly with the
 # batch).  Reads match the algorithmic bytes; the write figure is low because up to an L2's worth of dirty lines
 # has not been written back when the kernel ends.
-NCU_TRAFFIC = {"gn_silu_bwd": 536_964_608 + 226_946_048, "gn_silu_fwd": 268_459_520 + 210_318_592,
+NCU_TRAFFIC = {"gn_silu_bwd": 536_964_864 + 226_537_472, "gn_silu_fwd": 268_459_520 + 210_318_592,
                "ln_fwd": 2 * (134_267_904 + 83_640_064), "ln_bwd": 2 * (269_501_952 + 95_807_232)}
 
 
