@@ -55,6 +55,7 @@ static inline bool gn_path(int path, bool launched)
 
 }  // namespace b200
 
+#include "tma_desc.cuh"
 #include "groupnorm_strip.cuh"
 #include "groupnorm_dstrip.cuh"
 #include "groupnorm_ostrip.cuh"
@@ -434,15 +435,44 @@ static bool ostrip_fwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaS
         : pstrip_launch(GN_PATH_ONE_BARRIER, gn_fwd_ostrip<NT, VPT, ACT, MB, false, 2>, done[3], pgrid, NT, smem, s, args...);
 }
 
-template <int NT, int VPT, int ACT, class... Args>
-static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaStream_t s, Args... args)
+// Backward one-barrier strips.  On request (tunable "gn_bwd_tma") whole strips are staged by TMA: one box per
+// warp, tensor and strip out of a tensor map over the [B * HW, C] view of x and of dy, encoded here per launch.
+template <int NT, int VPT, int ACT>
+static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaStream_t s, float* dx, float* partials,
+    const float* dy, const float* x, const float* gamma, const float* beta, const float* mu, const float* rstd,
+    const StripGeom& g, int nitems, int B)
 {
-    static bool done[4][64] = {};
+    static bool done[6][64] = {};
+    CUtensorMap mx, md;
+    memset(&mx, 0, sizeof(mx));
+    memset(&md, 0, sizeof(md));
+    int* err = nullptr;
+    // "gn_bwd_tma": 0 (default) = cp.async staging; 1 = TMA for 512 x 8 strips with an activation; 2 = TMA wherever
+    // strips are whole (the measurements that keep it off by default are at gn_bwd_ostrip).
+    const int tma_mode = tune_get("gn_bwd_tma", 0);
+    if (full && (tma_mode == 2 || (tma_mode == 1 && ACT != ACT_IDENTITY && NT == 512 && VPT == 8))) {
+        const uint32_t box_rows = (uint32_t)(VPT * 32 / g.Q);
+        bool ok = planning_only();
+        if (!ok)
+            ok = make_tensor_map_2d(&mx, x, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct)
+                && make_tensor_map_2d(&md, dy, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct)
+                && (err = device_error_word()) != nullptr;
+        if (ok)
+            return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 1, true>, done[4], pgrid, NT, smem, s,
+                                  dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md)
+                            : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 2, true>, done[5], pgrid, NT, smem, s,
+                                  dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md);
+        err = nullptr;
+    }
     if (full)
-        return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 1>, done[0], pgrid, NT, smem, s, args...)
-                        : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 2>, done[1], pgrid, NT, smem, s, args...);
-    return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 1>, done[2], pgrid, NT, smem, s, args...)
-                    : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 2>, done[3], pgrid, NT, smem, s, args...);
+        return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 1, false>, done[0], pgrid, NT, smem, s,
+                              dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md)
+                        : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 2, false>, done[1], pgrid, NT, smem, s,
+                              dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md);
+    return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 1, false>, done[2], pgrid, NT, smem, s,
+                          dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md)
+                    : pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, false, 2, false>, done[3], pgrid, NT, smem, s,
+                          dx, partials, dy, x, gamma, beta, mu, rstd, g, nitems, err, mx, md);
 }
 
 #define OSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
@@ -452,7 +482,7 @@ static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaS
 #define OSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                 \
         return ostrip_bwd_launch<NTv, VPTv, ACT>(full, gpt, pgrid, osmem, s, dx, sc.partials, dy, x, gamma, beta, mu,  \
-                   rstd, plan.g, (int)grid)                                                                 \
+                   rstd, plan.g, (int)grid, B)                                                              \
             && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
 
 #define STRIP_FWD_CASE(NTv, VPTv)                                                                          \
@@ -573,7 +603,7 @@ static bool gn_backward_exact7(float* dx, float* dgamma, float* dbeta, const flo
     }
     const int gpt = ostrip_gpt(plan.g), nw = plan.NT / 32;
     const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
-        + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0);
+        + (size_t)(2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float) + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0) + 128;
     if (osmem > 226 * 1024)
         return false;
     Scratch sc;
@@ -689,8 +719,8 @@ static bool gn_backward_strip(float* dx, float* dgamma, float* dbeta, const floa
                 const int gpt = tune_get("gn_one_barrier", 1) ? ostrip_gpt(plan.g) : 0;
                 const int nw = plan.NT / 32;
                 const size_t osmem = (size_t)3 * plan.VPT * plan.NT * 16
-                    + (size_t)(2 * gpt * plan.NT + 2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float)
-                    + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0);
+                    + (size_t)(2 * C + 2 * plan.g.Gt * ostrip_row_floats(nw)) * sizeof(float)
+                    + (size_t)2 * nw * 2 * plan.g.Q * 16 + (plan.g.Q == 4 ? (size_t)nw * 1024 : 0) + 128;
                 // (a cluster barrier per strip, as in the forward kernel, was measured here too: 0.89 -> 0.78 with
                 // pairs, worse with wider clusters -- the backward has no idle time to absorb the lock step)
                 if (gpt && per_sm == 1 && osmem <= 226 * 1024 && per_cta >= tune_get("gn_one_barrier_min", 6)) {

@@ -72,6 +72,45 @@ __device__ __forceinline__ void cp_async_wait_pending(int n)
     }
 }
 
+// --- TMA staging of the backward strips (tensor maps: tma_desc.cuh) -----------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// One arrival that also announces `bytes` of asynchronous copies.  `after` is a value loaded from the buffer that
+// the copies will overwrite: naming it as an operand keeps the issue behind the return of that load (shared-memory
+// loads of a warp return in order, so behind all earlier ones too).
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes, float after)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes), "f"(after) : "memory");
+}
+// Box of the 2-D tensor map at (cx, cy) -> dense rows at dst; completion counts on bar.  No multicast.
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int cx, int cy, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(cx), "r"(cy), "r"(smem_addr(bar)) : "memory");
+}
+// Waits for the phase of the given parity, for at most about a second; after that the error word is set and
+// false returned (the caller stops waiting on anything and runs to its end).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err)
+{
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        if (ok)
+            return true;
+        if (clock64() - t0 > 2000000000LL) {
+            if (err)
+                atomicExch(err, 0x6e01);
+            return false;
+        }
+    }
+}
+
 // Lanes of a warp that share a group: Lg of them, this lane being number li (the same numbering in every
 // warp, so every warp derives bit-identical totals from the same partials).
 struct OStripLanes {
@@ -360,29 +399,54 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 
 // ---------------------------------------------------------------------------
 // backward (deep-staged: x double-buffered, dy single-buffered, as in gn_bwd_dstrip).
-// dynamic smem = xs[2][VPT][NT] float4 | ds[VPT][NT] float4 | mst[2*GPT][NT] | gamma[C] | beta[C]
+// dynamic smem = [pad to 128 B] xs[2][VPT][NT] float4 | ds[VPT][NT] float4 | gamma[C] | beta[C]
 //              | redg[2][Gt][ostrip_row_floats(NW)] | redc[2][NW][2][Q] float4 | wsum[NW][32][8] (Q == 4 only)
+//
+// mu and rstd of the next strip are fetched into registers one strip ahead (two or four plain loads per thread
+// and strip; staged through shared memory they cost a copy and a load each on the busiest queue).
+//
+// TMA = true (whole strips only): the strip's rows are dealt to the warps in contiguous blocks of VPT * 32 / Q
+// rows instead of interleaved, so that everything one warp reads of a tensor is ONE box of the 2-D tensor map
+// [B * HW rows, C] -- [VPT * 32 / Q rows, Ct channels], dense in shared memory in the warp's slot order.  Lane 0
+// of each warp issues the warp's three boxes (x twice, dy once) and every warp waits on its own mbarriers:
+// staging stays private to the warp as it is private to the thread without TMA, no CTA barrier is added, and
+// 16 of the about 70 shared-memory-queue entries per thread and strip disappear.
+// Measured on [256,32,32,256] with SiLU: alone in a loop 133 -> 126 us (0.92 -> 0.98 of the copy rate), after a
+// GroupNorm forward 152 -> 142 us, but after a LayerNorm forward 145 -> 169 us, and the benchmark step as a whole
+// 438 -> 472 us when it is the first thing a process times (460 -> 452 us at the end of the same process).
+// Without activation 125 -> 165 us alone; the 448 x 7 strips of [256,28,28,128] 55.6 -> 56.5 us.  So the
+// dispatcher uses it only on request.  Also measured: the interleaved row order kept and one box of 32 / Q rows
+// per row block (VPT boxes per warp and tensor): 141 us alone; the row blocks with cp.async: 132-135 us, as before.
 // ---------------------------------------------------------------------------
-template <int NT, int VPT, int ACT, bool FULL, int GPT>
+template <int NT, int VPT, int ACT, bool FULL, int GPT, bool TMA>
 __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, float* __restrict__ partials,
     const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ beta, const float* __restrict__ mu, const float* __restrict__ rstd, const StripGeom g,
-    const int nitems)
+    const int nitems, int* __restrict__ err, const __grid_constant__ CUtensorMap mapx,
+    const __grid_constant__ CUtensorMap mapdy)
 {
+    static_assert(!TMA || FULL, "boxes cover whole strips");
     pdl_prologue();
     constexpr int NW = NT / 32;
     constexpr int RG = ostrip_row_floats(NW);
+    constexpr uint32_t BOX_BYTES = VPT * 32 * 16;  // one box per warp, tensor and strip
     extern __shared__ float4 strip_stage[];
-    float4* xs = strip_stage;
+    __shared__ uint64_t mbar[TMA ? 3 * NW : 1];  // per warp: x parity 0, x parity 1, dy
+    float4* xs = strip_stage + ((128u - (smem_addr(strip_stage) & 127u)) & 127u) / 16u;
     float4* ds = xs + 2 * VPT * NT;
-    float* mst = reinterpret_cast<float*>(ds + VPT * NT);  // slot [2k][t] = mu, [2k+1][t] = rstd of this thread's group k
-    float* gsm = mst + 2 * GPT * NT;
+    float* gsm = reinterpret_cast<float*>(ds + VPT * NT);
     float* bsm = gsm + g.C;
     float* redg = bsm + g.C;
     float4* redc = reinterpret_cast<float4*>(redg + 2 * g.Gt * RG);
     float* wsum = reinterpret_cast<float*>(redc + 2 * NW * 2 * g.Q);  // [NW][32][8], used when Q == 4
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int q = t % g.Q, rl = t / g.Q;
+    const int q = t % g.Q;
+    const int RW = 32 / g.Q;  // rows of one warp-wide access
+    const int wrow0 = warp * RW * VPT;  // TMA: first row of this warp's block
+    const int rl = TMA ? wrow0 + lane / g.Q : t / g.Q;
+    const int slot0 = TMA ? warp * VPT * 32 + lane : t;  // slot of row block j: slot0 + j * SSTEP
+    constexpr int SSTEP = TMA ? 32 : NT;
+    const int brow = wrow0, bslot = warp * VPT * 32;  // the warp's box: first row in the sample, first slot in a buffer
     const int cb = 4 * q;
     const int M = GPT == 1 ? (g.cpg >> 2) : 1;
     const int gl = GPT == 1 ? q / M : 2 * q;
@@ -390,8 +454,10 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
     const OStripLanes ln = ostrip_lanes<GPT>(lane, q, g.Q, M);
     const float inv_n = 1.0f / ((float)g.HW * (float)g.cpg);
     const size_t rowoff = (size_t)rl * g.C + cb;
-    const size_t jstride = (size_t)g.RSTEP * g.C;
+    const size_t jstride = (size_t)(TMA ? RW : g.RSTEP) * g.C;
     const int G = gridDim.x;
+    uint64_t* const wbar = mbar + (TMA ? 3 * warp : 0);
+    bool alive = true;  // false once a bounded wait ran out: no more waits, the kernel runs to its end
 
     for (int i = t; i < g.C / 4; i += NT) {
         reinterpret_cast<float4*>(gsm)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);
@@ -399,26 +465,56 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             reinterpret_cast<float4*>(bsm)[i] = __ldg(reinterpret_cast<const float4*>(beta) + i);
     }
     int item = blockIdx.x;
-    {   // prologue: x(0) | dy(0) + statistics(0) | x(1)
+    float pmu[GPT], prs[GPT];  // statistics of the strip about to be processed
+#pragma unroll
+    for (int k = 0; k < GPT; ++k)
+        pmu[k] = prs[k] = 0.0f;
+    if (item < nitems) {
+        const int gi = (item / g.nct) * g.G + (item % g.nct) * g.Gt + gl;
+#pragma unroll
+        for (int k = 0; k < GPT; ++k) {
+            pmu[k] = __ldg(mu + gi + k);
+            prs[k] = __ldg(rstd + gi + k);
+        }
+    }
+    if constexpr (TMA) {  // prologue: x(0), dy(0), x(1)
+        if (lane == 0) {
+            mbar_init(wbar + 0, 1);
+            mbar_init(wbar + 1, 1);
+            mbar_init(wbar + 2, 1);
+            fence_mbar_init();
+            fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (item < nitems) {
+                const int cx = (item % g.nct) * g.Ct, cy = (item / g.nct) * g.HW + brow;
+                mbar_expect_tx(wbar + 0, BOX_BYTES, 0.0f);
+                tma_load_box(xs + bslot, &mapx, cx, cy, wbar + 0);
+                mbar_expect_tx(wbar + 2, BOX_BYTES, 0.0f);
+                tma_load_box(ds + bslot, &mapdy, cx, cy, wbar + 2);
+            }
+            if (item + G < nitems) {
+                const int it = item + G;
+                mbar_expect_tx(wbar + 1, BOX_BYTES, 0.0f);
+                tma_load_box(xs + VPT * NT + bslot, &mapx, (it % g.nct) * g.Ct, (it / g.nct) * g.HW + brow, wbar + 1);
+            }
+        }
+        __syncwarp();
+    } else {  // prologue: x(0) | dy(0) | x(1)
         const size_t o0 = dstrip_item_offset(g, item < nitems ? item : 0, rowoff);
         if (item < nitems) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&xs[j * NT + t], x + o0 + j * jstride);
+                    cp_async16(&xs[slot0 + j * SSTEP], x + o0 + j * jstride);
         }
         cp_async_commit();
         if (item < nitems) {
-            const int gi = (item / g.nct) * g.G + (item % g.nct) * g.Gt + gl;
-#pragma unroll
-            for (int k = 0; k < GPT; ++k) {
-                cp_async4(&mst[(2 * k) * NT + t], mu + gi + k);
-                cp_async4(&mst[(2 * k + 1) * NT + t], rstd + gi + k);
-            }
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&ds[j * NT + t], dy + o0 + j * jstride);
+                    cp_async16(&ds[slot0 + j * SSTEP], dy + o0 + j * jstride);
         }
         cp_async_commit();
         if (item + G < nitems) {
@@ -426,14 +522,15 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&xs[(VPT + j) * NT + t], x + o1 + j * jstride);
+                    cp_async16(&xs[VPT * NT + slot0 + j * SSTEP], x + o1 + j * jstride);
         }
         cp_async_commit();
     }
     __syncthreads();  // gamma / beta staged
 
     int par = 0;
-    for (; item < nitems; item += G, par ^= 1) {
+    uint32_t nstrip = 0;  // strips done by this CTA: the dy barrier is in phase nstrip & 1, x[par] in (nstrip >> 1) & 1
+    for (; item < nitems; item += G, par ^= 1, ++nstrip) {
         const int ctile = item % g.nct, b = item / g.nct;
         const int c0 = ctile * g.Ct;
         const size_t base = (size_t)b * g.HW * g.C + c0;
@@ -443,39 +540,50 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             be = *reinterpret_cast<const float4*>(bsm + c0 + cb);
         const bool more1 = item + G < nitems, more2 = item + 2 * G < nitems;
         const int it1 = more1 ? item + G : item;
+        const int it2 = more2 ? item + 2 * G : item;
         const float* n1 = dy + dstrip_item_offset(g, it1, rowoff);
-        const float* n2 = x + dstrip_item_offset(g, more2 ? item + 2 * G : item, rowoff);
+        const float* n2 = x + dstrip_item_offset(g, it2, rowoff);
         float4* xc = xs + par * VPT * NT;
 
-        cp_async_wait_but_one();
         float rsg[GPT], nmg[GPT];
 #pragma unroll
         for (int k = 0; k < GPT; ++k) {
-            rsg[k] = mst[(2 * k + 1) * NT + t];
-            nmg[k] = -mst[(2 * k) * NT + t] * rsg[k];
+            rsg[k] = prs[k];
+            nmg[k] = -pmu[k] * rsg[k];
         }
         if (more1) {
             const int gi = (it1 / g.nct) * g.G + (it1 % g.nct) * g.Gt + gl;
 #pragma unroll
             for (int k = 0; k < GPT; ++k) {
-                cp_async4(&mst[(2 * k) * NT + t], mu + gi + k);
-                cp_async4(&mst[(2 * k + 1) * NT + t], rstd + gi + k);
+                pmu[k] = __ldg(mu + gi + k);
+                prs[k] = __ldg(rstd + gi + k);
             }
+        }
+        if constexpr (TMA) {
+            if (alive)
+                alive = mbar_wait_bounded(wbar + 2, nstrip & 1u, err);
+        } else {
+            cp_async_wait_but_one();
         }
         float4 dv[VPT];
         const float* s1 = n1;
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {  // dy slots: read, then re-arm with strip i+1
+        for (int j = 0; j < VPT; ++j) {  // dy slots: read, then (cp.async form) re-arm with strip i+1
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
-            dv[j] = live ? lds128(&ds[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (more1 && live)
-                cp_async16(&ds[j * NT + t], s1);
+            dv[j] = live ? lds128(&ds[slot0 + j * SSTEP]) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!TMA && more1 && live)
+                cp_async16(&ds[slot0 + j * SSTEP], s1);
             s1 += jstride;
         }
-        cp_async_commit();
+        if constexpr (TMA) {
+            if (alive)
+                alive = mbar_wait_bounded(wbar + par, (nstrip >> 1) & 1u, err);
+        } else {
+            cp_async_commit();
+        }
         // xv becomes xhat, dv becomes dy * act'(z), both kept as packed pairs for the second phase.  The x slots of
-        // this parity are read one row block at a time, each re-armed with strip i+2 right behind its read and
-        // followed by its arithmetic, so that shared-memory traffic and arithmetic overlap within the warp.
+        // this parity are read one row block at a time, each (cp.async form) re-armed with strip i+2 right behind
+        // its read and followed by its arithmetic, so that shared-memory traffic and arithmetic overlap within the warp.
         const f32x2 rs01 = pk1(rsg[0]), rs23 = pk1(rsg[GPT - 1]), nm01 = pk1(nmg[0]), nm23 = pk1(nmg[GPT - 1]);
         const f32x2 ga01 = pk(ga.x, ga.y), ga23 = pk(ga.z, ga.w), be01 = pk(be.x, be.y), be23 = pk(be.z, be.w);
         f32x2 xa[VPT], xb[VPT], da[VPT], db[VPT];
@@ -486,10 +594,19 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const bool live = FULL || rl + j * g.RSTEP < g.HW;
-                const float4 xv = live ? lds128(&xc[j * NT + t]) : make_float4(0.f, 0.f, 0.f, 0.f);
-                if (more2 && live)
-                    cp_async16(&xc[j * NT + t], s2);
+                const float4 xv = live ? lds128(&xc[slot0 + j * SSTEP]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (!TMA && more2 && live)
+                    cp_async16(&xc[slot0 + j * SSTEP], s2);
                 s2 += jstride;
+                if (TMA && j == (VPT > 1 ? 1 : 0)) {
+                    // every dy slot of the warp has been read (the last one is an operand below): the box of strip i+1
+                    __syncwarp();
+                    if (lane == 0 && more1) {
+                        fence_proxy_async();
+                        mbar_expect_tx(wbar + 2, BOX_BYTES, dv[VPT - 1].w);
+                        tma_load_box(ds + bslot, &mapdy, (it1 % g.nct) * g.Ct, (it1 / g.nct) * g.HW + brow, wbar + 2);
+                    }
+                }
                 xa[j] = pk_fma(pk(xv.x, xv.y), rs01, nm01);
                 xb[j] = pk_fma(pk(xv.z, xv.w), rs23, nm23);
                 da[j] = pk(dv[j].x, dv[j].y);
@@ -504,11 +621,21 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 a2 = pk_fma(da[j], xa[j], a2);
                 b2 = pk_fma(db[j], xb[j], b2);
             }
-            cp_async_commit();
             unpk(a1, sA.x, sA.y);
             unpk(b1, sA.z, sA.w);
             unpk(a2, sB.x, sB.y);
             unpk(b2, sB.z, sB.w);
+            if constexpr (TMA) {
+                // the sums depend on every x slot of this parity: the box of strip i+2 goes behind them
+                __syncwarp();
+                if (lane == 0 && more2) {
+                    fence_proxy_async();
+                    mbar_expect_tx(wbar + par, BOX_BYTES, sB.w);
+                    tma_load_box(xc + bslot, &mapx, (it2 % g.nct) * g.Ct, (it2 / g.nct) * g.HW + brow, wbar + par);
+                }
+            } else {
+                cp_async_commit();
+            }
         }
         float* rg = redg + par * g.Gt * RG;
         float4* rc = redc + (size_t)par * NW * 2 * g.Q;
@@ -614,7 +741,9 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             dst[g.C] = sa;
         }
     }
-    cp_async_wait_all();
+    if constexpr (!TMA)
+        cp_async_wait_all();
+    // (TMA: every box issued was also waited for, unless a wait ran out)
 }
 
 }  // namespace b200
