@@ -240,7 +240,7 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
                 StripGeom g;
                 g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = rstep;
                 g.Gt = Ct / cpg; g.nct = C / Ct;
-                g.paced = 0;
+                g.paced = 0; g.hint = 0;
                 out->g = g;
                 const int red = (Q <= 32 && 32 % Q == 0) ? 2 * (NT / 32) * Ct : 2 * NT * 4;
                 out->smem = (size_t)(red + 2 * Ct + 2 * g.Gt) * sizeof(float);
@@ -452,10 +452,11 @@ static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaS
     const int tma_mode = tune_get("gn_bwd_tma", 0);
     if (full && (tma_mode == 2 || (tma_mode == 1 && ACT != ACT_IDENTITY && NT == 512 && VPT == 8))) {
         const uint32_t box_rows = (uint32_t)(VPT * 32 / g.Q);
+        const int l2p = tune_get("gn_bwd_tma_l2", 0);
         bool ok = planning_only();
         if (!ok)
-            ok = make_tensor_map_2d(&mx, x, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct)
-                && make_tensor_map_2d(&md, dy, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct)
+            ok = make_tensor_map_2d(&mx, x, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct, l2p)
+                && make_tensor_map_2d(&md, dy, (uint64_t)B * g.HW, (uint64_t)g.C, box_rows, (uint32_t)g.Ct, l2p)
                 && (err = device_error_word()) != nullptr;
         if (ok)
             return gpt == 1 ? pstrip_launch(GN_PATH_ONE_BARRIER, gn_bwd_ostrip<NT, VPT, ACT, true, 1, true>, done[4], pgrid, NT, smem, s,
@@ -477,11 +478,11 @@ static bool ostrip_bwd_launch(bool full, int gpt, long pgrid, size_t smem, cudaS
 
 #define OSTRIP_FWD_CASE(NTv, VPTv, MBv)                                                                     \
     if (plan.NT == NTv && plan.VPT == VPTv && per_sm == MBv)                                                \
-        return ostrip_fwd_launch<NTv, VPTv, ACT, MBv>(full, gpt, pgrid, osmem, s, y, mu, rstd, x, gamma, beta, plan.g, \
+        return plan.g.hint = tune_get("gn_fwd_l2_hint", fwd_hint_default), ostrip_fwd_launch<NTv, VPTv, ACT, MBv>(full, gpt, pgrid, osmem, s, y, mu, rstd, x, gamma, beta, plan.g, \
             eps, (int)grid);
 #define OSTRIP_BWD_CASE(NTv, VPTv)                                                                          \
     if (plan.NT == NTv && plan.VPT == VPTv)                                                                 \
-        return ostrip_bwd_launch<NTv, VPTv, ACT>(full, gpt, pgrid, osmem, s, dx, sc.partials, dy, x, gamma, beta, mu,  \
+        return plan.g.hint = tune_get("gn_bwd_l2_hint", 0), ostrip_bwd_launch<NTv, VPTv, ACT>(full, gpt, pgrid, osmem, s, dx, sc.partials, dy, x, gamma, beta, mu,  \
                    rstd, plan.g, (int)grid, B)                                                              \
             && (fold_partials(dgamma, dbeta, sc.partials, B, 2 * C, C, s), true);
 
@@ -522,7 +523,7 @@ static bool exact7_plan(StripPlan* out, int HW, int C, int G, int NT)
         StripGeom g;
         g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = NT / Q;
         g.Gt = Ct / cpg; g.nct = C / Ct;
-        g.paced = 0;
+        g.paced = 0; g.hint = 0;
         out->NT = NT;
         out->VPT = 7;
         out->g = g;
@@ -569,6 +570,9 @@ static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, 
     const bool full = true;
     plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
     // (clusters of 4 as for the 1024-thread strips: [256,28,28,256] 0.83 -> 0.80, so none here)
+    // staged loads marked evict_last: [256,28,28,128] forward 35.8 -> 34.6 us (0.88 -> 0.91), [128,28,28,64] 11.4 -> 11.3 us;
+    // on the power-of-two strips it changes nothing measurable, so there the default priority stays
+    const int fwd_hint_default = 1;
     OSTRIP_FWD_CASE(896, 7, 1) OSTRIP_FWD_CASE(448, 7, 2)
     return false;
 }
@@ -657,6 +661,7 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                     const bool clustered = cw > 1 && per_sm == 1 && full && plan.g.nct % cw == 0 && per_cta >= 8;
                     ClusterScope cluster(clustered ? cw : 1);
                     plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
+                    const int fwd_hint_default = 0;
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
                 }
@@ -759,7 +764,7 @@ static bool cstrip_plan(StripPlan* out, int HW, int C, int G)
     StripGeom g;
     g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = best; g.Q = best / 4; g.RSTEP = NT / g.Q;
     g.Gt = best / cpg; g.nct = C / best;
-    g.paced = 0;
+    g.paced = 0; g.hint = 0;
     out->NT = NT;
     out->VPT = 0;
     out->g = g;

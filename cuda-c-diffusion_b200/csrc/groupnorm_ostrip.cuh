@@ -43,6 +43,24 @@ namespace b200 {
 // [256,28,28,128] 10 %: four groups per warp read their rows at once).
 __host__ __device__ constexpr int ostrip_row_floats(int nw) { return (2 * nw + 4) | 4; }
 
+// L2 priority of the staged loads (StripGeom::hint).  A strip's row pieces are 64 or 128 bytes of rows whose
+// neighbouring pieces are read by the neighbouring CTAs a little earlier or later, so how long a fetched line
+// (and what DRAM delivered with it) survives in L2 decides how much of DRAM's work is shared between neighbours.
+__device__ __forceinline__ uint64_t l2_policy(int hint)
+{
+    uint64_t p;
+    if (hint == 1)
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    else if (hint == 2)
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    else
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void cp_async16_hint(void* smem_dst, const void* gmem_src, uint64_t policy)
+{
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
@@ -87,10 +105,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes, fl
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes), "f"(after) : "memory");
 }
 // Box of the 2-D tensor map at (cx, cy) -> dense rows at dst; completion counts on bar.  No multicast.
-__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int cx, int cy, uint64_t* bar)
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int cx, int cy, uint64_t* bar, uint64_t policy)
 {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_addr(dst)), "l"(map), "r"(cx), "r"(cy), "r"(smem_addr(bar)) : "memory");
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(cx), "r"(cy), "r"(smem_addr(bar)), "l"(policy) : "memory");
 }
 // Waits for the phase of the given parity, for at most about a second; after that the error word is set and
 // false returned (the caller stops waiting on anything and runs to its end).
@@ -214,6 +232,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
     const float* __restrict__ beta, const StripGeom g, const float eps, const int nitems)
 {
     pdl_prologue();
+    const uint64_t pol = l2_policy(g.hint);
     constexpr int NW = NT / 32;
     constexpr int RG = ostrip_row_floats(NW);
     extern __shared__ float4 strip_stage[];
@@ -257,7 +276,7 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             if (FULL || rl + j * g.RSTEP < g.HW)
-                cp_async16(&stage[j * NT + t], src);
+                cp_async16_hint(&stage[j * NT + t], src, pol);
             src += jstride;
             if (paced && j + 1 < VPT)
                 cp_async_commit();  // one group per slot (the caller commits the last)
@@ -427,6 +446,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 {
     static_assert(!TMA || FULL, "boxes cover whole strips");
     pdl_prologue();
+    const uint64_t pol = l2_policy(g.hint);
     constexpr int NW = NT / 32;
     constexpr int RG = ostrip_row_floats(NW);
     constexpr uint32_t BOX_BYTES = VPT * 32 * 16;  // one box per warp, tensor and strip
@@ -490,14 +510,14 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             if (item < nitems) {
                 const int cx = (item % g.nct) * g.Ct, cy = (item / g.nct) * g.HW + brow;
                 mbar_expect_tx(wbar + 0, BOX_BYTES, 0.0f);
-                tma_load_box(xs + bslot, &mapx, cx, cy, wbar + 0);
+                tma_load_box(xs + bslot, &mapx, cx, cy, wbar + 0, pol);
                 mbar_expect_tx(wbar + 2, BOX_BYTES, 0.0f);
-                tma_load_box(ds + bslot, &mapdy, cx, cy, wbar + 2);
+                tma_load_box(ds + bslot, &mapdy, cx, cy, wbar + 2, pol);
             }
             if (item + G < nitems) {
                 const int it = item + G;
                 mbar_expect_tx(wbar + 1, BOX_BYTES, 0.0f);
-                tma_load_box(xs + VPT * NT + bslot, &mapx, (it % g.nct) * g.Ct, (it / g.nct) * g.HW + brow, wbar + 1);
+                tma_load_box(xs + VPT * NT + bslot, &mapx, (it % g.nct) * g.Ct, (it / g.nct) * g.HW + brow, wbar + 1, pol);
             }
         }
         __syncwarp();
@@ -507,14 +527,14 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&xs[slot0 + j * SSTEP], x + o0 + j * jstride);
+                    cp_async16_hint(&xs[slot0 + j * SSTEP], x + o0 + j * jstride, pol);
         }
         cp_async_commit();
         if (item < nitems) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&ds[slot0 + j * SSTEP], dy + o0 + j * jstride);
+                    cp_async16_hint(&ds[slot0 + j * SSTEP], dy + o0 + j * jstride, pol);
         }
         cp_async_commit();
         if (item + G < nitems) {
@@ -522,7 +542,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
 #pragma unroll
             for (int j = 0; j < VPT; ++j)
                 if (FULL || rl + j * g.RSTEP < g.HW)
-                    cp_async16(&xs[VPT * NT + slot0 + j * SSTEP], x + o1 + j * jstride);
+                    cp_async16_hint(&xs[VPT * NT + slot0 + j * SSTEP], x + o1 + j * jstride, pol);
         }
         cp_async_commit();
     }
@@ -572,7 +592,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
             const bool live = FULL || rl + j * g.RSTEP < g.HW;
             dv[j] = live ? lds128(&ds[slot0 + j * SSTEP]) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (!TMA && more1 && live)
-                cp_async16(&ds[slot0 + j * SSTEP], s1);
+                cp_async16_hint(&ds[slot0 + j * SSTEP], s1, pol);
             s1 += jstride;
         }
         if constexpr (TMA) {
@@ -596,7 +616,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 const bool live = FULL || rl + j * g.RSTEP < g.HW;
                 const float4 xv = live ? lds128(&xc[slot0 + j * SSTEP]) : make_float4(0.f, 0.f, 0.f, 0.f);
                 if (!TMA && more2 && live)
-                    cp_async16(&xc[slot0 + j * SSTEP], s2);
+                    cp_async16_hint(&xc[slot0 + j * SSTEP], s2, pol);
                 s2 += jstride;
                 if (TMA && j == (VPT > 1 ? 1 : 0)) {
                     // every dy slot of the warp has been read (the last one is an operand below): the box of strip i+1
@@ -604,7 +624,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                     if (lane == 0 && more1) {
                         fence_proxy_async();
                         mbar_expect_tx(wbar + 2, BOX_BYTES, dv[VPT - 1].w);
-                        tma_load_box(ds + bslot, &mapdy, (it1 % g.nct) * g.Ct, (it1 / g.nct) * g.HW + brow, wbar + 2);
+                        tma_load_box(ds + bslot, &mapdy, (it1 % g.nct) * g.Ct, (it1 / g.nct) * g.HW + brow, wbar + 2, pol);
                     }
                 }
                 xa[j] = pk_fma(pk(xv.x, xv.y), rs01, nm01);
@@ -631,7 +651,7 @@ __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, f
                 if (lane == 0 && more2) {
                     fence_proxy_async();
                     mbar_expect_tx(wbar + par, BOX_BYTES, sB.w);
-                    tma_load_box(xc + bslot, &mapx, (it2 % g.nct) * g.Ct, (it2 / g.nct) * g.HW + brow, wbar + par);
+                    tma_load_box(xc + bslot, &mapx, (it2 % g.nct) * g.Ct, (it2 / g.nct) * g.HW + brow, wbar + par, pol);
                 }
             } else {
                 cp_async_commit();

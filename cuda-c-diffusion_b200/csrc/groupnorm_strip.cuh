@@ -82,6 +82,7 @@ __device__ __forceinline__ void strip_fold(float* red, float* chan, int Q, int C
 struct StripGeom {
     int HW, C, G, cpg, Ct, Q, RSTEP, Gt, nct;
     int paced;  // one-barrier forward without activation: release stores as the next strip's loads land
+    int hint;   // one-barrier kernels: L2 priority of the staged loads (0 normal, 1 evict_last, 2 evict_first)
     // (Starting the second CTA of every SM half a strip period late, so that the two run out of phase, was
     // measured: no effect.)
 };

@@ -30,7 +30,7 @@ static inline TensorMapEncodeTiledFn tensor_map_encoder()
 // Matrix [rows, cols] of fp32 at `base` (16-byte aligned, cols a multiple of 4); boxes of [box_rows, box_cols]
 // (each at most 256, box_cols a multiple of 4) land in shared memory densely, row-major, unswizzled.
 static inline bool make_tensor_map_2d(CUtensorMap* map, const float* base, uint64_t rows, uint64_t cols,
-    uint32_t box_rows, uint32_t box_cols)
+    uint32_t box_rows, uint32_t box_cols, int l2_promotion = 0)
 {
     TensorMapEncodeTiledFn enc = tensor_map_encoder();
     if (!enc || box_rows == 0 || box_rows > 256 || box_cols == 0 || box_cols > 256 || (box_cols & 3u) != 0
@@ -41,7 +41,9 @@ static inline bool make_tensor_map_2d(CUtensorMap* map, const float* base, uint6
     cuuint32_t box[2] = { box_cols, box_rows };
     cuuint32_t estride[2] = { 1, 1 };
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstride, box, estride,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        l2_promotion == 3 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+            : l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
