@@ -436,6 +436,10 @@ __global__ void __launch_bounds__(NT, MB) gn_fwd_ostrip(float* __restrict__ y, f
 // Without activation 125 -> 165 us alone; the 448 x 7 strips of [256,28,28,128] 55.6 -> 56.5 us.  So the
 // dispatcher uses it only on request.  Also measured: the interleaved row order kept and one box of 32 / Q rows
 // per row block (VPT boxes per warp and tensor): 141 us alone; the row blocks with cp.async: 132-135 us, as before.
+// What the boxes' lines do in L2 decides the rest (StripGeom::hint, tensor-map L2 promotion): evict_first 161 us
+// alone; promotion to 128 or 256 bytes 123.4 us alone (1.00 of the copy rate) but 469-472 us for the step;
+// evict_last 123.3-126 us alone and, for the step, 429 us on one GPU and 451-459 us on another of the same
+// pool, where the cp.async form gives 438-441 us on every one.
 // ---------------------------------------------------------------------------
 template <int NT, int VPT, int ACT, bool FULL, int GPT, bool TMA>
 __global__ void __launch_bounds__(NT, 1) gn_bwd_ostrip(float* __restrict__ dx, float* __restrict__ partials,
