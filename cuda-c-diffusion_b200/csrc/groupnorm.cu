@@ -240,7 +240,7 @@ static bool strip_plan(StripPlan* out, int B, int HW, int C, int G, int max_vpt,
                 StripGeom g;
                 g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = rstep;
                 g.Gt = Ct / cpg; g.nct = C / Ct;
-                g.paced = 0; g.hint = 0;
+                g.paced = 0; g.hint = tune_get("gn_strip_l2_hint", 0);
                 out->g = g;
                 const int red = (Q <= 32 && 32 % Q == 0) ? 2 * (NT / 32) * Ct : 2 * NT * 4;
                 out->smem = (size_t)(red + 2 * Ct + 2 * g.Gt) * sizeof(float);
@@ -523,7 +523,7 @@ static bool exact7_plan(StripPlan* out, int HW, int C, int G, int NT)
         StripGeom g;
         g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = Ct; g.Q = Q; g.RSTEP = NT / Q;
         g.Gt = Ct / cpg; g.nct = C / Ct;
-        g.paced = 0; g.hint = 0;
+        g.paced = 0; g.hint = tune_get("gn_strip_l2_hint", 0);
         out->NT = NT;
         out->VPT = 7;
         out->g = g;
@@ -570,8 +570,8 @@ static bool gn_forward_exact7(float* y, float* mu, float* rstd, const float* x, 
     const bool full = true;
     plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
     // (clusters of 4 as for the 1024-thread strips: [256,28,28,256] 0.83 -> 0.80, so none here)
-    // staged loads marked evict_last: [256,28,28,128] forward 35.8 -> 34.6 us (0.88 -> 0.91), [128,28,28,64] 11.4 -> 11.3 us;
-    // on the power-of-two strips it changes nothing measurable, so there the default priority stays
+    // staged loads marked evict_last: [256,28,28,256] forward 76.4 -> 66.7 us (0.82 -> 0.94), [256,28,28,128] 35.8 -> 34.6 us
+    // (0.88 -> 0.91), [128,28,28,64] 11.4 -> 11.3 us
     const int fwd_hint_default = 1;
     OSTRIP_FWD_CASE(896, 7, 1) OSTRIP_FWD_CASE(448, 7, 2)
     return false;
@@ -661,7 +661,10 @@ static bool gn_forward_strip(float* y, float* mu, float* rstd, const float* x, c
                     const bool clustered = cw > 1 && per_sm == 1 && full && plan.g.nct % cw == 0 && per_cta >= 8;
                     ClusterScope cluster(clustered ? cw : 1);
                     plan.g.paced = per_cta >= 8;  // paced stores in the kernels without activation
-                    const int fwd_hint_default = 0;
+                    // staged loads marked evict_last: [256,32,32,128] 50.7 -> 46.5 us (0.81 -> 0.88); [256,32,32,256] (in
+                    // clusters) and [256,16,16,256] within 1 % either way.  (In the backward and in the pipelined and
+                    // chunked kernels -- tunables "gn_bwd_l2_hint", "gn_strip_l2_hint" -- nothing moved by more than 1 %.)
+                    const int fwd_hint_default = 1;
                     OSTRIP_FWD_CASE(1024, 4, 1) OSTRIP_FWD_CASE(1024, 8, 1)
                     OSTRIP_FWD_CASE(512, 4, 2) OSTRIP_FWD_CASE(512, 8, 2)
                 }
@@ -764,7 +767,7 @@ static bool cstrip_plan(StripPlan* out, int HW, int C, int G)
     StripGeom g;
     g.HW = HW; g.C = C; g.G = G; g.cpg = cpg; g.Ct = best; g.Q = best / 4; g.RSTEP = NT / g.Q;
     g.Gt = best / cpg; g.nct = C / best;
-    g.paced = 0; g.hint = 0;
+    g.paced = 0; g.hint = tune_get("gn_strip_l2_hint", 0);
     out->NT = NT;
     out->VPT = 0;
     out->g = g;

@@ -26,13 +26,14 @@ template <int NT, int VPT, int NTENS>
 __device__ __forceinline__ void cstrip_prefetch(float4* stage, const StripGeom& g, size_t base, int row0, int rl,
     const float* __restrict__ t0, const float* __restrict__ t1)
 {
+    const uint64_t pol = l2_policy(g.hint);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int r = row0 + rl + j * g.RSTEP;
         if (r < g.HW) {
-            cp_async16(&stage[j * NT + threadIdx.x], t0 + base + (size_t)r * g.C);
+            cp_async16_hint(&stage[j * NT + threadIdx.x], t0 + base + (size_t)r * g.C, pol);
             if (NTENS == 2)
-                cp_async16(&stage[(VPT + j) * NT + threadIdx.x], t1 + base + (size_t)r * g.C);
+                cp_async16_hint(&stage[(VPT + j) * NT + threadIdx.x], t1 + base + (size_t)r * g.C, pol);
         }
     }
     cp_async_commit();

@@ -43,24 +43,6 @@ namespace b200 {
 // [256,28,28,128] 10 %: four groups per warp read their rows at once).
 __host__ __device__ constexpr int ostrip_row_floats(int nw) { return (2 * nw + 4) | 4; }
 
-// L2 priority of the staged loads (StripGeom::hint).  A strip's row pieces are 64 or 128 bytes of rows whose
-// neighbouring pieces are read by the neighbouring CTAs a little earlier or later, so how long a fetched line
-// (and what DRAM delivered with it) survives in L2 decides how much of DRAM's work is shared between neighbours.
-__device__ __forceinline__ uint64_t l2_policy(int hint)
-{
-    uint64_t p;
-    if (hint == 1)
-        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    else if (hint == 2)
-        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    else
-        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ void cp_async16_hint(void* smem_dst, const void* gmem_src, uint64_t policy)
-{
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "l"(policy) : "memory");
-}
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");

@@ -82,7 +82,7 @@ __device__ __forceinline__ void strip_fold(float* red, float* chan, int Q, int C
 struct StripGeom {
     int HW, C, G, cpg, Ct, Q, RSTEP, Gt, nct;
     int paced;  // one-barrier forward without activation: release stores as the next strip's loads land
-    int hint;   // one-barrier kernels: L2 priority of the staged loads (0 normal, 1 evict_last, 2 evict_first)
+    int hint;   // pipelined and one-barrier kernels: L2 priority of the staged loads (0 normal, 1 evict_last, 2 evict_first)
     // (Starting the second CTA of every SM half a strip period late, so that the two run out of phase, was
     // measured: no effect.)
 };
@@ -300,6 +300,24 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
 }
+// L2 priority of the staged loads (StripGeom::hint).  A strip's row pieces are 64 or 128 bytes of rows whose
+// neighbouring pieces are read by the neighbouring CTAs a little earlier or later, so how long a fetched line
+// (and what DRAM delivered with it) survives in L2 decides how much of DRAM's work is shared between neighbours.
+__device__ __forceinline__ uint64_t l2_policy(int hint)
+{
+    uint64_t p;
+    if (hint == 1)
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    else if (hint == 2)
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    else
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void cp_async16_hint(void* smem_dst, const void* gmem_src, uint64_t policy)
+{
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
@@ -309,13 +327,14 @@ __device__ __forceinline__ void strip_prefetch(float4* stage, const StripGeom& g
 {
     const int ctile = item % g.nct, b = item / g.nct;
     const size_t base = (size_t)b * g.HW * g.C + (size_t)ctile * g.Ct + 4 * q;
+    const uint64_t pol = l2_policy(g.hint);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int r = rl + j * g.RSTEP;
         if (r < g.HW) {
-            cp_async16(&stage[j * NT + threadIdx.x], t0 + base + (size_t)r * g.C);
+            cp_async16_hint(&stage[j * NT + threadIdx.x], t0 + base + (size_t)r * g.C, pol);
             if (NTENS == 2)
-                cp_async16(&stage[(VPT + j) * NT + threadIdx.x], t1 + base + (size_t)r * g.C);
+                cp_async16_hint(&stage[(VPT + j) * NT + threadIdx.x], t1 + base + (size_t)r * g.C, pol);
         }
     }
     cp_async_commit();
