@@ -15,10 +15,10 @@
 //   * the reduction buffers alternate with the strip parity, which is what makes the single barrier
 //     sufficient (a buffer is rewritten two strips later, after every thread has passed the barrier
 //     in between);
-//   * everything a strip needs from global memory besides the strip itself arrives through the
-//     staging pipeline, in slots owned by the thread that reads them: the shift of the forward pass
-//     (row 0 of the group's first channel) and mu/rstd of the backward pass (which come from DRAM, a
-//     microsecond away); gamma and beta of all C channels are copied to shared memory once per CTA;
+//   * everything a strip needs from global memory besides the strip itself is fetched a strip ahead by
+//     the thread that uses it: the shift of the forward pass (row 0 of the group's first channel) through
+//     the staging pipeline, mu/rstd of the backward pass (which come from DRAM, a microsecond away) into
+//     registers; gamma and beta of all C channels are copied to shared memory once per CTA;
 //   * the backward's per-channel sums (dgamma/dbeta partial rows) are still written per warp, but they
 //     are added up by Ct threads AFTER those threads have issued their dx stores: off the critical path.
 //
