@@ -86,7 +86,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes, fl
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes), "f"(after) : "memory");
 }
-// Box of the 2-D tensor map at (cx, cy) -> dense rows at dst; completion counts on bar.  No multicast.
+// Box of the 2-D tensor map at (cx, cy) -> dense rows at dst; completion counts on bar.  One CTA's own load.
 __device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int cx, int cy, uint64_t* bar, uint64_t policy)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
