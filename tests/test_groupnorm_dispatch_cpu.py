@@ -79,3 +79,17 @@ def test_register_resident_shapes_never_fall_to_the_chunked_or_generic_kernels(d
         if got["family"] in ("chunked", "generic"):
             bad.append(((B, HW, C, C // cpg, act, bwd), got["family"]))
     assert not bad, bad[:10]
+
+
+def test_tma_staging_is_a_request_and_keeps_the_geometry(describe):
+    """The backward's TMA staging is off by default; asked for, the dispatcher still plans the same one-barrier
+    launch (same CTAs, strip width and shared memory), and planning encodes no tensor map (no driver call)."""
+    lib = capi.load()
+    shape = (256, 1024, 256, 32, SILU, True)
+    plain = describe(*shape)
+    lib.b200_tune_set(b"gn_bwd_tma", 2)
+    try:
+        asked = describe(*shape)
+    finally:
+        lib.b200_tune_set(b"gn_bwd_tma", 0)
+    assert plain["family"] == "one-barrier" and asked == plain
